@@ -1,0 +1,34 @@
+/*
+ * rocfft_b200_ext.h — entry points of librocfft.so that have no counterpart in
+ * the reference's rocfft.h.  They exist for inspection and testing; a program
+ * written against rocfft.h alone never needs them.
+ */
+#ifndef ROCFFT_B200_EXT_H
+#define ROCFFT_B200_EXT_H
+
+#include "rocfft/rocfft.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Text description of a plan: one line per kernel launch with the kernel name,
+ * the buffers it reads and writes, tile counts and strides.  The same text
+ * rocfft_plan_get_print writes to stdout (reference: library/src/plan.cpp:3147,
+ * plan log layer at :3757-3914), returned in a caller buffer instead. */
+ROCFFT_EXPORT rocfft_status b200fft_plan_describe(const rocfft_plan plan, char* buf, size_t len);
+
+/* Host copy of the stacked per-pass twiddle table a Stockham kernel with the
+ * given factor list reads (reference layout: library/src/twiddles.cpp:68-106).
+ * precision 0 = float pairs, 1 = double pairs.  *needed receives the byte size. */
+ROCFFT_EXPORT rocfft_status b200fft_stacked_twiddles(
+    int n, const int* factors, int nfactors, int precision, void* out, size_t out_bytes, size_t* needed);
+
+/* Enumerates the function pool (reference: library/src/include/function_pool.h:44-272). */
+ROCFFT_EXPORT rocfft_status b200fft_pool_query(
+    size_t index, int* length, int* precision, int* variant, int* factors8, size_t* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

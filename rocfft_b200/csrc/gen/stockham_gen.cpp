@@ -1,0 +1,318 @@
+// Offline Stockham kernel generator for sm_100a.
+//
+// Build-time host program:   stockham_gen <output-dir> [--files K]
+//
+// Role in the reference: library/src/device/kernel-generator.py:223-984 (the
+// table of supported lengths with their factors / threads-per-transform /
+// workgroup sizes), library/src/device/generator/stockham_aot.cpp (the driver
+// that turns the table into kernels) and the generated function_pool.cpp
+// (kernel-generator.py:156-186).  The reference compiles its kernels at run
+// time with hipRTC and tunes them through a solution map; this generator
+// decides everything ahead of time and emits CUDA that nvcc compiles once.
+//
+// Outputs into <output-dir>:
+//   gen_butterflies.cuh    straight-line radix butterflies (see butterfly_emit.h)
+//   gen_kernels_<i>.cu     instantiations of the Stockham tile engine + C launchers
+//   gen_pool.cpp           the function pool: a table keyed by
+//                          (length, precision, variant) with launch metadata
+#include "butterfly_emit.h"
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <set>
+#include <string>
+#include <vector>
+
+namespace
+{
+    // radices the pass engine may use; each gets a generated butterfly
+    const std::vector<int> kRadices = {2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16};
+
+    // lengths with a single-kernel implementation; `small` selects a short
+    // list for quick bring-up builds
+    bool             g_small = false;
+    std::vector<int> supported_lengths()
+    {
+        std::set<int> s;
+        for(int n = 2; n <= 4096; n *= 2)
+            s.insert(n);
+        if(g_small)
+        {
+            for(int n : {3, 5, 6, 7, 9, 10, 11, 12, 13, 15, 20, 25, 27, 49, 50, 100, 125, 160, 200, 243, 500, 1000})
+                s.insert(n);
+            return std::vector<int>(s.begin(), s.end());
+        }
+        const int extra[] = {3,   5,   6,   7,   9,   10,  11,  12,  13,  14,  15,  18,  20,   21,
+                             22,  24,  25,  26,  27,  28,  30,  33,  35,  36,  39,  40,  42,   44,
+                             45,  48,  49,  50,  52,  54,  55,  56,  60,  63,  65,  70,  72,   75,
+                             77,  78,  80,  81,  84,  88,  90,  91,  96,  98,  99,  100, 104,  108,
+                             110, 112, 117, 120, 121, 125, 126, 130, 135, 140, 143, 144, 150,  160,
+                             162, 168, 169, 175, 176, 180, 192, 196, 200, 208, 216, 224, 225,  240,
+                             243, 250, 256, 270, 288, 300, 320, 324, 336, 343, 360, 375, 384,  400,
+                             432, 448, 480, 486, 500, 540, 576, 600, 625, 640, 648, 672, 675,  720,
+                             729, 750, 768, 800, 864, 896, 900, 960, 972, 1000, 1080, 1125, 1152, 1200,
+                             1215, 1250, 1280, 1296, 1344, 1350, 1440, 1458, 1500, 1536, 1600, 1620, 1728, 1792,
+                             1800, 1875, 1920, 1944, 2000, 2025, 2160, 2187, 2250, 2304, 2400, 2430, 2500, 2560,
+                             2592, 2700, 2880, 2916, 3000, 3072, 3125, 3200, 3240, 3375, 3456, 3600, 3645, 3750,
+                             3840, 3888, 4000, 4050};
+        for(int n : extra)
+            s.insert(n);
+        return std::vector<int>(s.begin(), s.end());
+    }
+
+    // choose a factorisation: fewest passes, then smallest largest radix,
+    // then smallest radix sum; every radix from kRadices and <= rmax
+    struct Choice
+    {
+        std::vector<int> f;
+        bool             ok = false;
+    };
+    bool better(const std::vector<int>& a, const std::vector<int>& b)
+    {
+        if(a.size() != b.size())
+            return a.size() < b.size();
+        int ma = *std::max_element(a.begin(), a.end()), mb = *std::max_element(b.begin(), b.end());
+        if(ma != mb)
+            return ma < mb;
+        int sa = 0, sb = 0;
+        for(int v : a)
+            sa += v;
+        for(int v : b)
+            sb += v;
+        return sa < sb;
+    }
+    std::map<std::pair<int, int>, Choice> memo;
+    Choice                                factorise(int n, int rmax)
+    {
+        auto key = std::make_pair(n, rmax);
+        auto it  = memo.find(key);
+        if(it != memo.end())
+            return it->second;
+        Choice best;
+        if(n == 1)
+        {
+            best.ok = true;
+            memo[key] = best;
+            return best;
+        }
+        for(int r : kRadices)
+        {
+            if(r > rmax || n % r)
+                continue;
+            Choice sub = factorise(n / r, rmax);
+            if(!sub.ok)
+                continue;
+            std::vector<int> f = sub.f;
+            f.push_back(r);
+            std::sort(f.begin(), f.end(), std::greater<int>());
+            if(!best.ok || better(f, best.f))
+            {
+                best.f  = f;
+                best.ok = true;
+            }
+        }
+        memo[key] = best;
+        return best;
+    }
+
+    struct Variant
+    {
+        const char* tag; // part of the kernel name
+        int         id; // value stored in the pool (see launch.h)
+        bool        col;
+        const char* iok;
+        const char* cin;
+        const char* cout_;
+    };
+    // ids must match enum b200fft_variant in launch/launch.h
+    const Variant kVariants[] = {
+        {"row_unit", 0, false, "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        {"row_gen", 1, false, "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
+        {"col_str", 2, true, "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
+        {"col_gen", 3, true, "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
+        {"row_tout", 4, false, "IO_STRIDED", "COOP_NONE", "COOP_CFAST"},
+        {"col_rout", 5, true, "IO_STRIDED", "COOP_NONE", "COOP_EFAST"},
+    };
+
+    struct Kernel
+    {
+        std::string      name;
+        int              n, prec, variant, tpt, tpb, minb;
+        std::vector<int> f;
+        size_t           smem;
+        std::string      cfg; // the KCfg<...> type
+    };
+
+    size_t smem_bytes(int n, int tpb, bool col, int prec, bool coop, int npass)
+    {
+        const int es   = prec == 0 ? 8 : 16;
+        const int ps   = prec == 0 ? 4 : 3;
+        const int npad = col ? n : ((n + (n >> ps)) | 1);
+        if(npass == 1 && !coop)
+            return 0;
+        return (size_t)es * npad * tpb + (coop ? 16 * tpb : 0);
+    }
+}
+
+int main(int argc, char** argv)
+{
+    if(argc < 2)
+    {
+        fprintf(stderr, "usage: %s <output-dir> [--files K] [--small]\n", argv[0]);
+        return 2;
+    }
+    std::string outdir = argv[1];
+    int         nfiles = 16;
+    for(int i = 2; i < argc; ++i)
+    {
+        if(!strcmp(argv[i], "--files") && i + 1 < argc)
+            nfiles = atoi(argv[i + 1]);
+        if(!strcmp(argv[i], "--small"))
+            g_small = true;
+    }
+
+    // ---- butterflies ----
+    {
+        std::ofstream o(outdir + "/gen_butterflies.cuh");
+        o << "// GENERATED by stockham_gen — do not edit.\n#pragma once\n"
+             "#include \"fft_types.cuh\"\nnamespace b200fft {\n\n";
+        gen::ButterflyEmitter em;
+        for(int r : kRadices)
+            o << em.emit(r);
+        o << "} // namespace b200fft\n\n// every radix above, for code that wants to visit them all\n"
+             "#define B200FFT_RADIX_LIST(X)";
+        for(int r : kRadices)
+            o << " X(" << r << ")";
+        o << "\n";
+    }
+
+    // ---- kernel table ----
+    std::vector<Kernel> kernels;
+    const size_t        smem_cap = 200 * 1024;
+    for(int prec = 0; prec < 2; ++prec)
+    {
+        const char* tname = prec == 0 ? "float" : "double";
+        for(int n : supported_lengths())
+        {
+            Choice ch = factorise(n, 16);
+            if(!ch.ok)
+                continue;
+            const int ept = *std::max_element(ch.f.begin(), ch.f.end());
+            const int tpt = n / ept;
+            for(const Variant& v : kVariants)
+            {
+                const bool coop = strcmp(v.cin, "COOP_NONE") || strcmp(v.cout_, "COOP_NONE");
+                int        tpb;
+                if(v.col)
+                {
+                    tpb = prec == 0 ? 16 : 8;
+                    while(tpb > 1
+                          && (tpt * tpb > 1024
+                              || smem_bytes(n, tpb, true, prec, coop, (int)ch.f.size()) > smem_cap))
+                        tpb /= 2;
+                    // a column tile narrower than 32 bytes gains nothing over the row kernel
+                    if(tpb * (prec == 0 ? 8 : 16) < 32)
+                        continue;
+                    if(tpt * tpb > 1024)
+                        continue;
+                }
+                else
+                {
+                    int target = coop ? 256 : 256;
+                    tpb        = std::max(1, std::min(64, target / tpt));
+                    if(coop)
+                        tpb = std::max(tpb, prec == 0 ? 16 : 8); // transposed stores need a wide tile
+                    while(tpb > 1
+                          && (tpt * tpb > 1024
+                              || smem_bytes(n, tpb, false, prec, coop, (int)ch.f.size()) > smem_cap))
+                        tpb /= 2;
+                    if(tpt * tpb > 1024)
+                        continue;
+                    if(coop && tpb * (prec == 0 ? 8 : 16) < 32)
+                        continue;
+                }
+                size_t sm = smem_bytes(n, tpb, v.col, prec, coop, (int)ch.f.size());
+                if(sm > smem_cap)
+                    continue;
+                const int threads = tpt * tpb;
+                // register budget: data + twiddles + temporaries
+                const int regs_est = (prec == 0 ? 3 : 6) * ept + 40;
+                int       minb     = std::max(1, 65536 / (threads * std::min(regs_est, 255)));
+                if(sm)
+                    minb = std::min<int>(minb, (int)(220 * 1024 / (sm + 1024)));
+                minb = std::max(1, std::min(minb, 2048 / threads));
+                minb = std::min(minb, 8);
+
+                Kernel k;
+                k.n       = n;
+                k.prec    = prec;
+                k.variant = v.id;
+                k.tpt     = tpt;
+                k.tpb     = tpb;
+                k.minb    = minb;
+                k.f       = ch.f;
+                k.smem    = sm;
+                k.name    = std::string("fft_") + (prec == 0 ? "sp" : "dp") + "_len" + std::to_string(n)
+                         + "_" + v.tag;
+                std::string fl = "FactorList<";
+                for(size_t i = 0; i < ch.f.size(); ++i)
+                    fl += (i ? "," : "") + std::to_string(ch.f[i]);
+                fl += ">";
+                k.cfg = std::string("KCfg<") + tname + "," + std::to_string(n) + ","
+                        + std::to_string(tpt) + "," + std::to_string(tpb) + ","
+                        + (v.col ? "true" : "false") + "," + v.iok + "," + v.cin + "," + v.cout_ + ","
+                        + std::to_string(minb) + "," + fl + ">";
+                kernels.push_back(k);
+            }
+        }
+    }
+
+    // ---- kernel sources, spread over nfiles translation units ----
+    // order by length descending so that expensive kernels spread evenly
+    std::vector<size_t> order(kernels.size());
+    for(size_t i = 0; i < order.size(); ++i)
+        order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
+        return kernels[a].n > kernels[b].n;
+    });
+    std::vector<std::ofstream> files(nfiles);
+    for(int i = 0; i < nfiles; ++i)
+    {
+        files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
+        files[i] << "// GENERATED by stockham_gen — do not edit.\n"
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_engine.cuh\"\nusing namespace b200fft;\n\n";
+    }
+    for(size_t oi = 0; oi < order.size(); ++oi)
+    {
+        const Kernel& k = kernels[order[oi]];
+        auto&         o = files[oi % nfiles];
+        o << "extern \"C\" cudaError_t b200fft_launch_" << k.name
+          << "(const b200fft_kargs* a, unsigned long long ntiles, cudaStream_t s)\n{\n"
+          << "    return launch_tile_kernel<" << k.cfg << ">(*a, ntiles, s);\n}\n\n";
+    }
+
+    // ---- function pool ----
+    {
+        std::ofstream o(outdir + "/gen_pool.cpp");
+        o << "// GENERATED by stockham_gen — do not edit.\n#include \"launch.h\"\n\n";
+        for(const Kernel& k : kernels)
+            o << "extern \"C\" cudaError_t b200fft_launch_" << k.name
+              << "(const b200fft_kargs*, unsigned long long, cudaStream_t);\n";
+        o << "\nstatic const b200fft_pool_entry kPool[] = {\n";
+        for(const Kernel& k : kernels)
+        {
+            o << "    {" << k.n << ", " << k.prec << ", " << k.variant << ", " << k.tpt << ", " << k.tpb
+              << ", " << k.tpt * k.tpb << ", " << k.f.size() << ", {";
+            for(size_t i = 0; i < 8; ++i)
+                o << (i ? "," : "") << (i < k.f.size() ? k.f[i] : 0);
+            o << "}, " << k.smem << "ull, b200fft_launch_" << k.name << ", \"" << k.name << "\"},\n";
+        }
+        o << "};\n\nextern \"C\" const b200fft_pool_entry* b200fft_pool(size_t* count)\n{\n"
+             "    *count = sizeof(kPool) / sizeof(kPool[0]);\n    return kPool;\n}\n";
+    }
+    fprintf(stderr, "stockham_gen: %zu kernels in %d files\n", kernels.size(), nfiles);
+    return 0;
+}

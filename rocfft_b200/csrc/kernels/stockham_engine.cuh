@@ -1,0 +1,449 @@
+// Stockham autosort FFT engine for sm_100a: one CTA transforms a tile of TPB
+// batched 1D transforms of compile-time length N held in shared memory.
+//
+// Role in the reference: library/src/device/generator/stockham_gen_base.h:642-918
+// (the generated kernel body), stockham_gen_rr.h / _cc.h / _rc.h / _cr.h (the
+// four tiling modes: row/column input x row/column output) and the
+// load/twiddle/butterfly/store generators at :347-456.  This file is the
+// hand-written device-side half; the offline generator instantiates it with
+// explicit factor lists and supplies the straight-line butterflies.
+//
+// Pass structure (same decomposition the reference uses, restated):
+//   pass p has radix W = F[p], height CH = F[0]*...*F[p-1], NB = N/W butterflies.
+//   butterfly b reads points b + j*NB (j < W), multiplies point j >= 1 by
+//   exp(-2 pi i * j * (b mod CH) / (CH*W)), runs the radix-W DFT and writes
+//   result j to (b div CH)*W*CH + (b mod CH) + j*CH.  After the last pass the
+//   data is in natural order.
+//
+// Thread mapping:
+//   ROW tiles:  thread = c*TPT + t   (c = transform in tile, t = lane in transform),
+//               shared layout [c][pad(e)], coalesced along the transform.
+//   COL tiles:  thread = t*TPB + c,  shared layout [e][c], coalesced across the
+//               TPB adjacent transforms (column FFTs of 2D/3D data).
+//   Pass 0 reads global memory straight into registers and the last pass
+//   writes registers straight to global memory, so a kernel makes one HBM
+//   round trip; optional cooperative stages re-map threads for transposing
+//   loads/stores.
+#pragma once
+#include "fft_types.cuh"
+#include "kargs.h"
+#include <cuda_runtime.h>
+
+namespace b200fft
+{
+    // compile-time factor list
+    template <int... F>
+    struct FactorList
+    {
+        static constexpr int count = sizeof...(F);
+        __host__ __device__ static constexpr int get(int i)
+        {
+            constexpr int v[] = {F...};
+            return v[i];
+        }
+        __host__ __device__ static constexpr int cum(int i)
+        {
+            int c = 1;
+            for(int k = 0; k < i; ++k)
+                c *= get(k);
+            return c;
+        }
+        // offset of pass p's block inside the stacked twiddle table
+        // (pass 0 has no twiddles; pass p holds (W-1)*CH entries)
+        __host__ __device__ static constexpr int tw_offset(int p)
+        {
+            int o = 0;
+            for(int k = 1; k < p; ++k)
+                o += (get(k) - 1) * cum(k);
+            return o;
+        }
+    };
+
+    enum IoKind
+    {
+        IO_UNIT    = 0, // interleaved complex, unit stride along the transform (both sides)
+        IO_STRIDED = 1, // interleaved complex, run-time strides
+        IO_GENERIC = 2, // interleaved or planar chosen at run time, run-time strides
+    };
+    enum CoopKind
+    {
+        COOP_NONE  = 0, // pass threads touch global memory themselves
+        COOP_EFAST = 1, // staged through shared memory, consecutive threads walk a transform
+        COOP_CFAST = 2, // staged, consecutive threads walk across the tile's transforms
+    };
+
+    // Kernel configuration; instantiated by generated code.
+    template <typename T_,
+              int  N_,
+              int  TPT_,
+              int  TPB_,
+              bool COL_,
+              int  IOK_,
+              int  CIN_,
+              int  COUT_,
+              int  MINB_,
+              class FL_>
+    struct KCfg
+    {
+        using T  = T_;
+        using T2 = typename cx<T_>::type;
+        using FL = FL_;
+        static constexpr int  N       = N_;
+        static constexpr int  TPT     = TPT_;
+        static constexpr int  TPB     = TPB_;
+        static constexpr bool COL     = COL_;
+        static constexpr int  IOK     = IOK_;
+        static constexpr int  CIN     = CIN_;
+        static constexpr int  COUT    = COUT_;
+        static constexpr int  MINB    = MINB_;
+        static constexpr int  THREADS = TPT_ * TPB_;
+        static constexpr int  NPASS   = FL_::count;
+        // row layout: one pad element every 128 bytes, and an odd row pitch so
+        // that walking across rows is conflict-free as well
+        static constexpr int PADSHIFT = (sizeof(T_) == 4) ? 4 : 3;
+        static constexpr int NPAD     = COL_ ? N_ : ((N_ + (N_ >> PADSHIFT)) | 1);
+        static constexpr int SMEM_ELEMS = COL_ ? N_ * TPB_ : NPAD * TPB_;
+        static constexpr bool NEEDS_SMEM = (NPASS > 1) || CIN_ != COOP_NONE || COUT_ != COOP_NONE;
+        static constexpr size_t SMEM_BYTES
+            = NEEDS_SMEM ? sizeof(T2) * (size_t)SMEM_ELEMS + (CIN_ != COOP_NONE || COUT_ != COOP_NONE ? 16 * TPB_ : 0)
+                         : 0;
+
+        __device__ static __forceinline__ int sidx(int c, int e)
+        {
+            if constexpr(COL_)
+                return e * TPB_ + c;
+            else
+                return c * NPAD + e + (e >> PADSHIFT);
+        }
+    };
+
+    // ------------------------------------------------------------------
+    // global-memory element access
+    // ------------------------------------------------------------------
+    template <class C>
+    __device__ __forceinline__ typename C::T2
+        gload(const b200fft_ioview& v, long long base, int e, bool inverse)
+    {
+        using T  = typename C::T;
+        using T2 = typename C::T2;
+        T2 r;
+        if constexpr(C::IOK == IO_UNIT)
+        {
+            r = reinterpret_cast<const T2*>(v.p[0])[base + e];
+        }
+        else if constexpr(C::IOK == IO_STRIDED)
+        {
+            r = reinterpret_cast<const T2*>(v.p[0])[base + (long long)e * v.es];
+        }
+        else
+        {
+            const long long off = base + (long long)e * v.es;
+            if(v.planar)
+            {
+                r.x = reinterpret_cast<const T*>(v.p[0])[off];
+                r.y = reinterpret_cast<const T*>(v.p[1])[off];
+            }
+            else
+                r = reinterpret_cast<const T2*>(v.p[0])[off];
+        }
+        return inverse ? cswap(r) : r;
+    }
+
+    template <class C>
+    __device__ __forceinline__ void gstore(const b200fft_ioview& v,
+                                           long long             base,
+                                           int                   e,
+                                           typename C::T2        val,
+                                           bool                  inverse,
+                                           bool                  use_scale,
+                                           typename C::T         scale)
+    {
+        using T  = typename C::T;
+        using T2 = typename C::T2;
+        if(inverse)
+            val = cswap(val);
+        if(use_scale)
+        {
+            val.x *= scale;
+            val.y *= scale;
+        }
+        if constexpr(C::IOK == IO_UNIT)
+        {
+            reinterpret_cast<T2*>(v.p[0])[base + e] = val;
+        }
+        else if constexpr(C::IOK == IO_STRIDED)
+        {
+            reinterpret_cast<T2*>(v.p[0])[base + (long long)e * v.es] = val;
+        }
+        else
+        {
+            const long long off = base + (long long)e * v.es;
+            if(v.planar)
+            {
+                reinterpret_cast<T*>(v.p[0])[off] = val.x;
+                reinterpret_cast<T*>(v.p[1])[off] = val.y;
+            }
+            else
+                reinterpret_cast<T2*>(v.p[0])[off] = val;
+        }
+    }
+
+    // ------------------------------------------------------------------
+    // one radix pass
+    // ------------------------------------------------------------------
+    template <class C, int P, class LD, class ST>
+    __device__ __forceinline__ void
+        run_pass(const int t, LD ld, ST st, const typename C::T2* __restrict__ tw, const bool sync_mid)
+    {
+        using T2          = typename C::T2;
+        constexpr int W   = C::FL::get(P);
+        constexpr int CH  = C::FL::cum(P);
+        constexpr int NB  = C::N / W;
+        constexpr int BPT = (NB + C::TPT - 1) / C::TPT;
+        constexpr bool FULL = (NB % C::TPT) == 0;
+        constexpr int TWO = C::FL::tw_offset(P);
+
+        T2 x[BPT][W];
+#pragma unroll
+        for(int i = 0; i < BPT; ++i)
+        {
+            const int b = t + i * C::TPT;
+            if(FULL || b < NB)
+            {
+#pragma unroll
+                for(int j = 0; j < W; ++j)
+                    x[i][j] = ld(b + j * NB);
+            }
+        }
+        if(sync_mid)
+            __syncthreads();
+#pragma unroll
+        for(int i = 0; i < BPT; ++i)
+        {
+            const int b = t + i * C::TPT;
+            if(FULL || b < NB)
+            {
+                const int k = b % CH;
+                if constexpr(P > 0)
+                {
+#pragma unroll
+                    for(int j = 1; j < W; ++j)
+                        x[i][j] = cmul(x[i][j], tw[TWO + (j - 1) * CH + k]);
+                }
+                Butterfly<W, T2>::run(x[i]);
+                const int base = (b / CH) * (W * CH) + k;
+#pragma unroll
+                for(int j = 0; j < W; ++j)
+                    st(base + j * CH, x[i][j]);
+            }
+        }
+    }
+
+    // Runs passes FIRST..NPASS-1 recursively.  `src`/`dst` are the first
+    // pass's loader and the last pass's storer; middle traffic goes through
+    // shared memory.  SRC_SMEM / DST_SMEM tell whether src / dst alias the
+    // shared tile (then barriers are needed around them).
+    template <class C, int P, bool SRC_SMEM, bool DST_SMEM, class SRC, class DST>
+    __device__ __forceinline__ void run_passes(const int                 t,
+                                               const int                 c,
+                                               typename C::T2*           sm,
+                                               const typename C::T2* __restrict__ tw,
+                                               SRC                       src,
+                                               DST                       dst)
+    {
+        using T2                 = typename C::T2;
+        constexpr bool first     = (P == 0);
+        constexpr bool last      = (P == C::NPASS - 1);
+        auto           sm_load   = [=](int e) -> T2 { return sm[C::sidx(c, e)]; };
+        auto           sm_store  = [=](int e, T2 v) { sm[C::sidx(c, e)] = v; };
+        constexpr bool rd_smem   = first ? SRC_SMEM : true;
+        constexpr bool wr_smem   = last ? DST_SMEM : true;
+        constexpr bool sync_mid  = rd_smem && wr_smem;
+
+        if constexpr(first && last)
+            run_pass<C, P>(t, src, dst, tw, sync_mid);
+        else if constexpr(first)
+            run_pass<C, P>(t, src, sm_store, tw, sync_mid);
+        else if constexpr(last)
+            run_pass<C, P>(t, sm_load, dst, tw, sync_mid);
+        else
+            run_pass<C, P>(t, sm_load, sm_store, tw, sync_mid);
+
+        if constexpr(wr_smem)
+            __syncthreads();
+        if constexpr(!last)
+            run_passes<C, P + 1, SRC_SMEM, DST_SMEM>(t, c, sm, tw, src, dst);
+    }
+
+    // ------------------------------------------------------------------
+    // tile bookkeeping
+    // ------------------------------------------------------------------
+    struct TilePos
+    {
+        unsigned i0_first; // first outer-0 index of the tile
+        unsigned i1, i2;
+    };
+
+    __device__ __forceinline__ TilePos decode_tile(const b200fft_kargs& a, unsigned tile, int tpb)
+    {
+        TilePos  p;
+        unsigned t0 = tile % a.ntile0;
+        unsigned r  = tile / a.ntile0;
+        p.i0_first  = t0 * (unsigned)tpb;
+        p.i1        = r % a.on[1];
+        p.i2        = r / a.on[1];
+        return p;
+    }
+
+    __device__ __forceinline__ long long
+        view_base(const b200fft_ioview& v, unsigned i0, unsigned i1, unsigned i2)
+    {
+        return (long long)i0 * v.os[0] + (long long)i1 * v.os[1] + (long long)i2 * v.os[2];
+    }
+
+    // ------------------------------------------------------------------
+    // the kernel
+    // ------------------------------------------------------------------
+    template <class C>
+    __global__ void __launch_bounds__(C::THREADS, C::MINB)
+        stockham_tile_kernel(const __grid_constant__ b200fft_kargs a)
+    {
+        using T  = typename C::T;
+        using T2 = typename C::T2;
+        extern __shared__ __align__(16) unsigned char smem_raw[];
+        T2* sm = reinterpret_cast<T2*>(smem_raw);
+
+        const int tid = threadIdx.x;
+        int       c, t;
+        if constexpr(C::COL)
+        {
+            c = tid % C::TPB;
+            t = tid / C::TPB;
+        }
+        else
+        {
+            c = tid / C::TPT;
+            t = tid % C::TPT;
+        }
+        const TilePos  tp      = decode_tile(a, blockIdx.x, C::TPB);
+        const bool     inverse = a.inverse != 0;
+        const bool     use_sc  = a.use_scale != 0;
+        const T        scale   = (T)a.scale;
+        const T2* __restrict__ tw = reinterpret_cast<const T2*>(a.twiddles);
+
+        // per-transform base offsets for cooperative stages
+        long long* bases = reinterpret_cast<long long*>(smem_raw + sizeof(T2) * (size_t)C::SMEM_ELEMS);
+        if constexpr(C::CIN != COOP_NONE || C::COUT != COOP_NONE)
+        {
+            if(tid < C::TPB)
+            {
+                bases[2 * tid]     = view_base(a.in, tp.i0_first + tid, tp.i1, tp.i2);
+                bases[2 * tid + 1] = view_base(a.out, tp.i0_first + tid, tp.i1, tp.i2);
+            }
+            __syncthreads();
+        }
+        const unsigned nvalid = min((unsigned)C::TPB, a.on[0] - tp.i0_first);
+
+        const bool      valid = (unsigned)c < nvalid;
+        const long long ibase = view_base(a.in, tp.i0_first + c, tp.i1, tp.i2);
+        const long long obase = view_base(a.out, tp.i0_first + c, tp.i1, tp.i2);
+
+        // ---- cooperative load stage ----
+        if constexpr(C::CIN != COOP_NONE)
+        {
+            for(int idx = tid; idx < C::N * C::TPB; idx += C::THREADS)
+            {
+                int cc, e;
+                if constexpr(C::CIN == COOP_EFAST)
+                {
+                    cc = idx / C::N;
+                    e  = idx % C::N;
+                }
+                else
+                {
+                    cc = idx % C::TPB;
+                    e  = idx / C::TPB;
+                }
+                T2 v;
+                v.x = 0;
+                v.y = 0;
+                if((unsigned)cc < nvalid)
+                    v = gload<C>(a.in, bases[2 * cc], e, inverse);
+                sm[C::sidx(cc, e)] = v;
+            }
+            __syncthreads();
+        }
+
+        auto g_src = [&](int e) -> T2 {
+            T2 v;
+            v.x = 0;
+            v.y = 0;
+            if(valid)
+                v = gload<C>(a.in, ibase, e, inverse);
+            return v;
+        };
+        auto g_dst = [&](int e, T2 v) {
+            if(valid)
+                gstore<C>(a.out, obase, e, v, inverse, use_sc, scale);
+        };
+        auto s_src = [=](int e) -> T2 { return sm[C::sidx(c, e)]; };
+        auto s_dst = [=](int e, T2 v) { sm[C::sidx(c, e)] = v; };
+
+        constexpr bool SI = C::CIN != COOP_NONE;
+        constexpr bool SO = C::COUT != COOP_NONE;
+        if constexpr(SI && SO)
+            run_passes<C, 0, true, true>(t, c, sm, tw, s_src, s_dst);
+        else if constexpr(SI)
+            run_passes<C, 0, true, false>(t, c, sm, tw, s_src, g_dst);
+        else if constexpr(SO)
+            run_passes<C, 0, false, true>(t, c, sm, tw, g_src, s_dst);
+        else
+            run_passes<C, 0, false, false>(t, c, sm, tw, g_src, g_dst);
+
+        // ---- cooperative store stage ----
+        if constexpr(C::COUT != COOP_NONE)
+        {
+            // run_passes ended with a barrier because the last pass wrote shared memory
+            for(int idx = tid; idx < C::N * C::TPB; idx += C::THREADS)
+            {
+                int cc, e;
+                if constexpr(C::COUT == COOP_EFAST)
+                {
+                    cc = idx / C::N;
+                    e  = idx % C::N;
+                }
+                else
+                {
+                    cc = idx % C::TPB;
+                    e  = idx / C::TPB;
+                }
+                if((unsigned)cc < nvalid)
+                    gstore<C>(a.out, bases[2 * cc + 1], e, sm[C::sidx(cc, e)], inverse, use_sc, scale);
+            }
+        }
+    }
+
+    // host-side launch helper used by generated launchers
+    template <class C>
+    cudaError_t launch_tile_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
+    {
+        static bool attr_done[64] = {};
+        int         dev           = 0;
+        cudaGetDevice(&dev);
+        if(C::SMEM_BYTES > 48 * 1024 && dev < 64 && !attr_done[dev])
+        {
+            cudaError_t e = cudaFuncSetAttribute(stockham_tile_kernel<C>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)C::SMEM_BYTES);
+            if(e != cudaSuccess)
+                return e;
+            attr_done[dev] = true;
+        }
+        if(ntiles == 0)
+            return cudaSuccess;
+        if(ntiles > 0x7fffffffull)
+            return cudaErrorInvalidConfiguration;
+        stockham_tile_kernel<C><<<(unsigned)ntiles, C::THREADS, C::SMEM_BYTES, stream>>>(a);
+        return cudaGetLastError();
+    }
+} // namespace b200fft

@@ -1,0 +1,74 @@
+// Thin C-ABI launch layer between the C++ planner and the CUDA kernels.
+//
+// Role in the reference: library/src/include/function_pool.h:44-272 (lookup of a
+// kernel by length / precision / scheme) and library/src/rtc_kernel.cpp:58-115
+// (packing arguments and launching).  The planner is plain C++ and never sees
+// a <<< >>> launch: it looks kernels up in the pool and calls the function
+// pointers below with plain structs, sizes and a stream.
+#ifndef B200FFT_LAUNCH_H
+#define B200FFT_LAUNCH_H
+
+#include "../kernels/kargs.h"
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Tiling / addressing variants of a Stockham kernel (reference schemes in
+// library/src/include/compute_scheme.h:29-83 given for orientation).
+typedef enum b200fft_variant
+{
+    B200FFT_ROW_UNIT = 0, // rows in, rows out, interleaved unit stride  (CS_KERNEL_STOCKHAM)
+    B200FFT_ROW_GEN  = 1, // rows, any stride / planar
+    B200FFT_COL_STR  = 2, // columns in, columns out, interleaved  (CS_KERNEL_STOCKHAM_BLOCK_CC)
+    B200FFT_COL_GEN  = 3, // columns, any stride / planar
+    B200FFT_ROW_TOUT = 4, // rows in, columns out (transposing store) (CS_KERNEL_STOCKHAM_BLOCK_RC)
+    B200FFT_COL_ROUT = 5, // columns in, rows out                     (CS_KERNEL_STOCKHAM_BLOCK_CR)
+} b200fft_variant;
+
+typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);
+
+typedef struct b200fft_pool_entry
+{
+    int                   length;
+    int                   precision; // 0 single, 1 double
+    int                   variant; // b200fft_variant
+    int                   tpt; // threads per transform
+    int                   tpb; // transforms per block (tile width)
+    int                   threads;
+    int                   nfactors;
+    int                   factors[8];
+    unsigned long long    smem_bytes;
+    b200fft_tile_launcher launch;
+    const char*           name;
+} b200fft_pool_entry;
+
+// generated table of every compiled Stockham kernel
+const b200fft_pool_entry* b200fft_pool(size_t* count);
+
+// ---- element-wise helper kernels (elementwise.cu) -------------------------
+// Every launcher enqueues on `stream` and returns the launch status.
+typedef enum b200fft_ew_kind
+{
+    B200FFT_EW_COPY_C2C = 0, // complex -> complex copy between layouts (optionally scaled)
+    B200FFT_EW_R2C_COPY, // real -> complex (imaginary part zero)
+    B200FFT_EW_C2R_COPY, // complex -> real (real part only)
+    B200FFT_EW_C2HERM_COPY, // first n/2+1 points of a complex row
+    B200FFT_EW_HERM2C_COPY, // Hermitian half -> full complex row
+    B200FFT_EW_R2C_POST, // even-length real forward post-processing
+    B200FFT_EW_C2R_PRE, // even-length real inverse pre-processing
+    B200FFT_EW_BLUE_PAD_MUL, // x * chirp, zero padded to M
+    B200FFT_EW_POINT_MUL, // row *= table
+    B200FFT_EW_BLUE_RES_MUL, // first n points of row * chirp
+    B200FFT_EW_LARGE_TWIDDLE, // row-major [n1][n2] tile *= W_n^(i1*i2)
+    B200FFT_EW_COUNT
+} b200fft_ew_kind;
+
+cudaError_t b200fft_launch_elementwise(int kind, int precision, const b200fft_eargs* a, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

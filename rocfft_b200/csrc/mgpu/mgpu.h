@@ -1,0 +1,22 @@
+// Multi-device layer: bricks, fields, slab decomposition and the global
+// transpose over NCCL / NVLink.
+//
+// Role in the reference: library/src/plan.cpp:490-696 (fields and bricks),
+// :1244-2358 (gather/scatter plans, the optimised multi-device plan and the
+// global transpose) and library/src/tree_node.cpp:473-928 (communication ops).
+#pragma once
+#include "../plan/plan.h"
+
+namespace b200fft
+{
+    // builds plan->mgpu from the in/out fields of the description; throws on
+    // malformed fields (std::runtime_error) so that creation reports failure
+    void          build_multi_device_plan(rocfft_plan_t* plan);
+    void          destroy_multi_device_plan(rocfft_plan_t* plan);
+    size_t        multi_device_work_bytes(const rocfft_plan_t* plan);
+    std::string   describe_multi_device_plan(const rocfft_plan_t* plan);
+    rocfft_status execute_multi_device_plan(rocfft_plan_t*                 plan,
+                                            void* const*                   in,
+                                            void* const*                   out,
+                                            const rocfft_execution_info_t* info);
+}

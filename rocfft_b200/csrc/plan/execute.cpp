@@ -1,0 +1,114 @@
+// Executor: resolves buffers and enqueues every step of a plan on a stream.
+//
+// Role in the reference: library/src/powX.cpp:525-957 (TransformPowX: choose
+// each kernel's input/output among user buffers and work-buffer segments, apply
+// offsets, launch) and library/src/transform.cpp:361-474 (ExecPlan::ExecuteAsync).
+// Nothing here synchronises: all work is asynchronous on the caller's stream.
+#include "plan.h"
+
+namespace b200fft
+{
+    namespace
+    {
+        inline char* bump(void* p, long long bytes)
+        {
+            return static_cast<char*>(p) + bytes;
+        }
+
+        bool resolve(const BufRef& b, void* const* in, void* const* out, void* work, void* p[2])
+        {
+            void* const* src = nullptr;
+            switch(b.id)
+            {
+            case BUF_USER_IN:
+                src = in;
+                break;
+            case BUF_USER_OUT:
+                src = out;
+                break;
+            case BUF_TEMP:
+                if(!work)
+                    return false;
+                p[0] = bump(work, (long long)b.byte_off[0]);
+                p[1] = nullptr;
+                return true;
+            }
+            if(!src || !src[0])
+                return false;
+            p[0] = bump(src[0], (long long)b.byte_off[0]);
+            p[1] = nullptr;
+            if(b.planar)
+            {
+                if(!src[1])
+                    return false;
+                p[1] = bump(src[1], (long long)b.byte_off[1]);
+            }
+            return true;
+        }
+
+    }
+
+    rocfft_status execute_core(const PlanCore& core,
+                               void* const*    in,
+                               void* const*    out,
+                               void*           work,
+                               cudaStream_t    stream)
+    {
+        if(core.host_only)
+            return rocfft_status_failure; // no CPU fallback exists
+        for(const Step& s : core.steps)
+        {
+            void *ip[2], *op[2];
+            if(!resolve(s.in, in, out, work, ip) || !resolve(s.out, in, out, work, op))
+                return rocfft_status_failure;
+
+            // host loops over dimensions the kernels do not index themselves
+            std::vector<size_t> idx(s.loops.size(), 0);
+            for(;;)
+            {
+                long long ioff = 0, ooff = 0;
+                for(size_t k = 0; k < s.loops.size(); ++k)
+                {
+                    ioff += (long long)idx[k] * s.loops[k].in_stride;
+                    ooff += (long long)idx[k] * s.loops[k].out_stride;
+                }
+                void* ipp[2] = {bump(ip[0], ioff * (long long)s.in_elem_bytes),
+                                ip[1] ? bump(ip[1], ioff * (long long)s.in_elem_bytes) : nullptr};
+                void* opp[2] = {bump(op[0], ooff * (long long)s.out_elem_bytes),
+                                op[1] ? bump(op[1], ooff * (long long)s.out_elem_bytes) : nullptr};
+                cudaError_t e;
+                if(s.kind == Step::EW)
+                {
+                    b200fft_eargs a = s.ea;
+                    a.in.p[0]       = ipp[0];
+                    a.in.p[1]       = ipp[1];
+                    a.out.p[0]      = opp[0];
+                    a.out.p[1]      = opp[1];
+                    e = b200fft_launch_elementwise(s.ew_kind, core.precision, &a, stream);
+                }
+                else
+                {
+                    b200fft_kargs a = s.ka;
+                    a.in.p[0]       = ipp[0];
+                    a.in.p[1]       = ipp[1];
+                    a.out.p[0]      = opp[0];
+                    a.out.p[1]      = opp[1];
+                    e = s.kern->launch(&a, s.ntiles, stream);
+                }
+                if(e != cudaSuccess)
+                    return rocfft_status_failure;
+
+                size_t k = 0;
+                for(; k < idx.size(); ++k)
+                {
+                    if(++idx[k] < s.loops[k].count)
+                        break;
+                    idx[k] = 0;
+                }
+                if(k == idx.size())
+                    break;
+            }
+        }
+        return rocfft_status_success;
+    }
+}

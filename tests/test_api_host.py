@@ -1,0 +1,181 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports every
+symbol the headers declare, argument validation returns the reference's status
+codes (library/src/plan.cpp:729-779, 2959-3074; transform.cpp:35-103), and the
+planner picks the intended kernels for the benchmark configurations."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import rocfft_b200 as rf
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L(built_library):
+    L = built_library
+    L.b200fft_plan_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+    rf.rocfft_setup()
+    return L
+
+
+def describe(L, plan):
+    buf = ctypes.create_string_buffer(1 << 16)
+    assert L.b200fft_plan_describe(plan.plan, buf, len(buf)) == 0
+    return buf.value.decode()
+
+
+def test_every_declared_symbol_is_exported(L):
+    declared = set()
+    for hdr in ("include/rocfft/rocfft.h", "include/rocfft_b200_ext.h"):
+        text = open(os.path.join(ROOT, hdr)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        declared |= set(re.findall(r"\b((?:rocfft|b200fft)_[a-z0-9_]+)\s*\(", text))
+    assert set(rf.EXPORTED_SYMBOLS) <= declared
+    for name in sorted(declared):
+        assert hasattr(L, name), f"{name} is declared but not exported"
+
+
+def test_version_string(L):
+    st, v = rf.rocfft_get_version_string(64)
+    assert st == rf.rocfft_status_success and v.startswith("1.0.32")
+    st, _ = rf.rocfft_get_version_string(4)
+    assert st == rf.rocfft_status_invalid_arg_value
+    assert L.rocfft_get_version_string(None, 10) == rf.rocfft_status_failure
+
+
+def test_dimension_limits(L):
+    st, p = rf.rocfft_plan_create(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward,
+                                  rf.rocfft_precision_single, [4, 4, 4, 4], 1)
+    assert st == rf.rocfft_status_invalid_dimensions
+    rf.rocfft_plan_destroy(p)
+
+
+def _layout_status(ttype, placement, it, ot):
+    st, d = rf.rocfft_plan_description_create()
+    rf.rocfft_plan_description_set_data_layout(d, it, ot, None, None, None, 0, None, 0)
+    st, p = rf.rocfft_plan_create(placement, ttype, rf.rocfft_precision_single, [16], 1, d)
+    rf.rocfft_plan_destroy(p)
+    rf.rocfft_plan_description_destroy(d)
+    return st
+
+
+def test_array_type_rules(L):
+    CI, CP, RE, HI, HP = (rf.rocfft_array_type_complex_interleaved, rf.rocfft_array_type_complex_planar,
+                          rf.rocfft_array_type_real, rf.rocfft_array_type_hermitian_interleaved,
+                          rf.rocfft_array_type_hermitian_planar)
+    F, I, RF, RI = (rf.rocfft_transform_type_complex_forward, rf.rocfft_transform_type_complex_inverse,
+                    rf.rocfft_transform_type_real_forward, rf.rocfft_transform_type_real_inverse)
+    ip, op = rf.rocfft_placement_inplace, rf.rocfft_placement_notinplace
+    bad = rf.rocfft_status_invalid_array_type
+    ok = rf.rocfft_status_success
+    assert _layout_status(F, op, CI, CP) == ok
+    assert _layout_status(F, ip, CI, CP) == bad  # in place needs identical formats
+    assert _layout_status(F, op, RE, CI) == bad
+    assert _layout_status(I, op, CI, HI) == bad
+    assert _layout_status(RF, op, RE, HP) == ok
+    assert _layout_status(RF, ip, RE, HP) == bad  # in place real forward must be interleaved
+    assert _layout_status(RF, op, CI, HI) == bad
+    assert _layout_status(RI, op, HP, RE) == ok
+    assert _layout_status(RI, ip, HP, RE) == bad
+    assert _layout_status(RI, op, HI, CI) == bad
+
+
+def test_scale_factor_must_be_finite(L):
+    st, d = rf.rocfft_plan_description_create()
+    assert rf.rocfft_plan_description_set_scale_factor(d, float("nan")) == rf.rocfft_status_invalid_arg_value
+    assert rf.rocfft_plan_description_set_scale_factor(d, float("inf")) == rf.rocfft_status_invalid_arg_value
+    assert rf.rocfft_plan_description_set_scale_factor(d, 0.5) == rf.rocfft_status_success
+    rf.rocfft_plan_description_destroy(d)
+
+
+def test_stride_count_must_match_rank(L):
+    st, d = rf.rocfft_plan_description_create()
+    rf.rocfft_plan_description_set_data_layout(d, rf.rocfft_array_type_complex_interleaved,
+                                               rf.rocfft_array_type_complex_interleaved, None, None, [1, 8, 64], 0,
+                                               None, 0)
+    st, p = rf.rocfft_plan_create(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward,
+                                  rf.rocfft_precision_single, [8, 8], 1, d)
+    assert st == rf.rocfft_status_invalid_strides
+    rf.rocfft_plan_destroy(p)
+    rf.rocfft_plan_description_destroy(d)
+
+
+def test_execution_info_contract(L):
+    st, info = rf.rocfft_execution_info_create()
+    assert st == rf.rocfft_status_success
+    assert rf.rocfft_execution_info_set_work_buffer(info, 0, 128) == rf.rocfft_status_invalid_work_buffer
+    one = ctypes.c_void_p(0)
+    arr = (ctypes.c_void_p * 1)(one)
+    assert L.rocfft_execution_info_set_load_callback(info, arr, arr, 16) == rf.rocfft_status_invalid_arg_value
+    assert L.rocfft_execution_info_set_store_callback(info, arr, arr, 0) == rf.rocfft_status_success
+    assert rf.rocfft_execution_info_destroy(info) == rf.rocfft_status_success
+    assert rf.rocfft_execution_info_destroy(None) == rf.rocfft_status_success
+    assert rf.rocfft_plan_description_destroy(None) == rf.rocfft_status_success
+    assert L.rocfft_execute(None, None, None, None) == rf.rocfft_status_failure
+
+
+def test_cache_exports_are_inert(L):
+    buf = ctypes.c_void_p()
+    n = ctypes.c_size_t(123)
+    assert L.rocfft_cache_serialize(ctypes.byref(buf), ctypes.byref(n)) == rf.rocfft_status_success
+    assert n.value == 0
+    assert L.rocfft_cache_deserialize(buf, 0) == rf.rocfft_status_success
+    assert L.rocfft_cache_buffer_free(buf) == rf.rocfft_status_success
+
+
+def test_planner_choices_for_benchmark_configs(L):
+    # config 1: one row kernel, no work buffer
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [4096], 16384)
+    text = describe(L, p)
+    assert "steps: 1" in text and "len4096" in text and p.work_bytes == 0
+    # config 3: row pass then in-place column pass, no transposes, no work buffer
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 64)
+    text = describe(L, p)
+    assert "steps: 2" in text and "col" in text and p.work_bytes == 0
+    # config 5: three in-place passes
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
+    assert "steps: 3" in describe(L, p) and p.work_bytes == 0
+    # config 4: prime length goes through Bluestein
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)
+    assert "bluestein" in describe(L, p)
+    assert p.work_bytes > 0
+
+
+def test_stacked_twiddle_table_matches_pass_model(L):
+    """Runs the Stockham pass structure the kernels implement (see
+    stockham_engine.cuh) in numpy with the library's own twiddle table and
+    compares with the oracle: validates table layout and index arithmetic."""
+    from oracle import fft_oracle as orc
+    L.b200fft_stacked_twiddles.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]
+    for n, factors in [(4096, [16, 16, 16]), (1000, [10, 10, 10]), (500, [10, 10, 5]), (60, [5, 4, 3]), (16, [16])]:
+        fa = (ctypes.c_int * len(factors))(*factors)
+        need = ctypes.c_size_t()
+        L.b200fft_stacked_twiddles(n, fa, len(factors), 1, None, 0, ctypes.byref(need))
+        tab = np.empty(need.value // 16, dtype=np.complex128)
+        L.b200fft_stacked_twiddles(n, fa, len(factors), 1, tab.ctypes.data, need.value, ctypes.byref(need))
+        x = orc.uniform_input((n,), np.complex128, seed=n)
+        cur = x.copy()
+        ch, off = 1, 0
+        for p, w in enumerate(factors):
+            nb = n // w
+            nxt = np.empty_like(cur)
+            for b in range(nb):
+                v = cur[b + np.arange(w) * nb].copy()
+                k = b % ch
+                if p > 0:
+                    for j in range(1, w):
+                        v[j] *= tab[off + (j - 1) * ch + k]
+                V = np.fft.fft(v)
+                base = (b // ch) * w * ch + k
+                nxt[base + np.arange(w) * ch] = V
+            if p > 0:
+                off += (w - 1) * ch
+            ch *= w
+            cur = nxt
+        ref = orc.c2c(x[None, :], -1)[0]
+        assert np.max(np.abs(cur - ref)) < 1e-11 * np.max(np.abs(ref)), (n, factors)
