@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Benchmark of the FFT hot path through the rocFFT-compatible C API.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...   # CPU baseline arm
+
+Headline workload (every N): the 3D complex-to-complex forward FFT
+1024 x 1024 x 1024, fp32 interleaved, in place (8 GiB) — the configuration that
+scales over 1/2/4/8 GPUs.  Metric: GFLOP/s = 5 * N * log2(N) / t with
+N = 2^30 (the definition rocfft-bench uses, clients/bench/bench.cpp:470-480).
+At N = 1 the line also carries, under "configs", the four single-GPU
+configurations (batched 1D c2c 4096, real 1000 forward/inverse, 2D fp64
+1024x1024, prime-length 10007) with their own GFLOP/s and HBM-roofline
+fractions.
+
+One JSON line is printed by rank 0.  Inputs are synthetic: iid uniform
+[-0.5, 0.5) per component from a seeded generator.  A scale factor 1/sqrt(N) is
+set on the plans so that repeated in-place steps stay finite; it is fused into
+the last kernel and removes no work.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "GFLOP/s (5*N*log2(N)/t), 3D c2c 1024^3 fp32 in-place"
+UNIT = "GFLOP/s"
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------
+# clock sampling during the timed region (read-only NVML queries)
+# --------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index=0, period=0.004):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+        self.index, self.period = index, period
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------
+def workloads():
+    import rocfft_b200 as rf
+    F, RF, RI = (rf.rocfft_transform_type_complex_forward, rf.rocfft_transform_type_real_forward,
+                 rf.rocfft_transform_type_real_inverse)
+    IP, OP = rf.rocfft_placement_inplace, rf.rocfft_placement_notinplace
+    lg = math.log2
+    return {
+        # name: (ttype, placement, precision, lengths, batch, in dtype, in elems, out dtype, out elems, flops)
+        "c2c_1d_4096x16384_fp32_ip": dict(tt=F, pl=IP, prec=0, lens=[4096], batch=16384, idt="complex64",
+                                          inel=4096 * 16384, odt="complex64", outel=4096 * 16384,
+                                          flops=5 * 4096 * 12 * 16384),
+        "r2c_1d_1000x65536_fp32": dict(tt=RF, pl=OP, prec=0, lens=[1000], batch=65536, idt="float32",
+                                       inel=1000 * 65536, odt="complex64", outel=501 * 65536,
+                                       flops=2.5 * 1000 * lg(1000) * 65536),
+        "c2r_1d_1000x65536_fp32": dict(tt=RI, pl=OP, prec=0, lens=[1000], batch=65536, idt="complex64",
+                                       inel=501 * 65536, odt="float32", outel=1000 * 65536,
+                                       flops=2.5 * 1000 * lg(1000) * 65536, hermitian=True),
+        "c2c_2d_1024x1024x64_fp64": dict(tt=F, pl=OP, prec=1, lens=[1024, 1024], batch=64, idt="complex128",
+                                         inel=64 << 20, odt="complex128", outel=64 << 20,
+                                         flops=5 * 2 ** 20 * 20 * 64),
+        "c2c_1d_10007x4096_fp32_bluestein": dict(tt=F, pl=OP, prec=0, lens=[10007], batch=4096, idt="complex64",
+                                                 inel=10007 * 4096, odt="complex64", outel=10007 * 4096,
+                                                 flops=5 * 10007 * lg(10007) * 4096),
+        "c2c_3d_1024x1024x1024_fp32_ip": dict(tt=F, pl=IP, prec=0, lens=[1024, 1024, 1024], batch=1,
+                                              idt="complex64", inel=1 << 30, odt="complex64", outel=1 << 30,
+                                              flops=5 * 2 ** 30 * 30),
+    }
+
+
+HEADLINE = "c2c_3d_1024x1024x1024_fp32_ip"
+
+
+def _np_dtype(name):
+    return np.dtype(name)
+
+
+def _fill_device(torch, dt, nelem, seed, hermitian_rows=None):
+    """Seeded uniform [-0.5, 0.5) input generated on the host in chunks (the
+    device only receives copies), returned as a flat device tensor."""
+    tdt = {"complex64": torch.complex64, "complex128": torch.complex128, "float32": torch.float32}[dt]
+    out = torch.empty(nelem, dtype=tdt, device="cuda")
+    rng = np.random.default_rng(seed)
+    chunk = 1 << 24
+    ndt = _np_dtype(dt)
+    for s in range(0, nelem, chunk):
+        n = min(chunk, nelem - s)
+        if ndt.kind == "c":
+            rdt = np.float32 if ndt == np.complex64 else np.float64
+            a = np.empty(n, dtype=ndt)
+            a.real = rng.random(n, dtype=np.float32 if rdt == np.float32 else np.float64) - 0.5
+            a.imag = rng.random(n, dtype=np.float32 if rdt == np.float32 else np.float64) - 0.5
+        else:
+            a = (rng.random(n, dtype=np.float32) - 0.5).astype(ndt)
+        out[s:s + n].copy_(torch.from_numpy(a))
+    if hermitian_rows:
+        # Hermitian rows need real DC and Nyquist bins to be a valid spectrum
+        v = out.view(-1, hermitian_rows)
+        v[:, 0] = v[:, 0].real.to(tdt)
+        v[:, -1] = v[:, -1].real.to(tdt)
+    return out
+
+
+def run_single_gpu(name, w, steps, warmup, peak, do_e2e=True, e2e_steps=None, sampler=None):
+    """Runs one workload on the current device; returns a result dict."""
+    import torch
+    import rocfft_b200 as rf
+
+    L = rf.lib()
+    L.b200fft_launch_count.restype = ctypes.c_ulonglong
+    L.b200fft_execute_profiled.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                           ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
+                                           ctypes.POINTER(ctypes.c_float), ctypes.c_size_t,
+                                           ctypes.POINTER(ctypes.c_size_t)]
+    L.b200fft_plan_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+
+    ntot = int(np.prod(w["lens"]))
+    ip = w["pl"] == rf.rocfft_placement_inplace
+    # unitary scaling keeps repeated steps finite; fused into the last kernel
+    scale = 1.0 / math.sqrt(ntot)
+    plan = rf.Plan(w["pl"], w["tt"], w["prec"], w["lens"], w["batch"], scale=scale)
+    x = _fill_device(torch, w["idt"], w["inel"], seed=1, hermitian_rows=(w["lens"][0] // 2 + 1) if w.get("hermitian") else None)
+    y = x if ip else torch.empty(w["outel"], dtype={"complex64": torch.complex64, "complex128": torch.complex128,
+                                                    "float32": torch.float32}[w["odt"]], device="cuda")
+    work = torch.empty(max(plan.work_bytes, 1), dtype=torch.uint8, device="cuda")
+    if plan.work_bytes:
+        assert plan.set_work_buffer(work.data_ptr(), plan.work_bytes) == 0
+    stream = torch.cuda.Stream()
+    plan.set_stream(stream.cuda_stream)
+    ins, outs = [x.data_ptr()], (None if ip else [y.data_ptr()])
+    in_bytes = w["inel"] * _np_dtype(w["idt"]).itemsize
+    out_bytes = w["outel"] * _np_dtype(w["odt"]).itemsize
+
+    def step():
+        st = plan.execute(ins, outs)
+        if st != 0:
+            raise RuntimeError(f"rocfft_execute failed: {st}")
+
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            step()
+        stream.synchronize()
+        launches0 = L.b200fft_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = int(L.b200fft_launch_count() - launches0)
+
+        # per-kernel times for the roofline of the dominant kernel
+        ins_a = (ctypes.c_void_p * 1)(ctypes.c_void_p(ins[0]))
+        outs_a = (ctypes.c_void_p * 1)(ctypes.c_void_p(outs[0])) if outs else None
+        step_ms = (ctypes.c_float * 64)()
+        nst = ctypes.c_size_t()
+        prof = np.zeros(64)
+        reps = 3
+        for _ in range(reps):
+            st = L.b200fft_execute_profiled(plan.plan, ins_a, outs_a, plan.info, step_ms, 64, ctypes.byref(nst))
+            assert st == 0
+            prof[:nst.value] += np.array(step_ms[:nst.value])
+        prof = prof[:nst.value] / reps
+    buf = ctypes.create_string_buffer(1 << 14)
+    L.b200fft_plan_describe(plan.plan, buf, len(buf))
+    kernel_names = [ln.split("]")[1].split()[0] for ln in buf.value.decode().splitlines() if ln.startswith("  [")]
+
+    res = {
+        "workload": name,
+        "ms_per_step": ms,
+        "gflops": w["flops"] / ms / 1e6,
+        "algorithmic_bytes": in_bytes + out_bytes,
+        "hbm_gbs": (in_bytes + out_bytes) / ms / 1e6,
+        "hbm_frac": (in_bytes + out_bytes) / ms / 1e6 / peak,
+        "kernels": [{"name": n, "ms": float(t)} for n, t in zip(kernel_names, prof)],
+        "launches_per_step": launches // max(steps, 1),
+        "gpu_launches": launches,
+        "work_buffer_bytes": plan.work_bytes,
+    }
+
+    if do_e2e:
+        # host buffers through the public API: H2D of the input, execute, D2H of the result
+        k = e2e_steps or steps
+        hin = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
+        hin.copy_(x.view(torch.uint8))
+        hout = hin if ip else torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
+        xb, yb = x.view(torch.uint8), y.view(torch.uint8)
+        with torch.cuda.stream(stream):
+            def e2e_step():
+                xb.copy_(hin, non_blocking=True)
+                step()
+                hout.copy_(yb, non_blocking=True)
+            e2e_step()
+            stream.synchronize()
+            t0 = time.perf_counter()
+            e0.record(stream)
+            for _ in range(k):
+                e2e_step()
+            e1.record(stream)
+            stream.synchronize()
+            wall = (time.perf_counter() - t0) * 1e3 / k
+            ems = e0.elapsed_time(e1) / k
+        res["e2e"] = {"value": w["flops"] / ems / 1e6, "unit": UNIT, "ms_per_step": ems, "wall_ms_per_step": wall,
+                      "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes}
+        del hin, hout
+    plan.destroy()
+    del x, y, work
+    torch.cuda.empty_cache()
+    return res
+
+
+# --------------------------------------------------------------------------
+# CPU baseline: pocketfft (scipy.fft) on the host cores, bounded sample
+# --------------------------------------------------------------------------
+def cpu_baseline_3d(budget_planes=32, cols=1 << 14):
+    """Times the oracle's CPU path (the port of the FFTW-style reference
+    transform) for the 1024^3 workload on a bounded sample: `budget_planes`
+    XY planes through a 2D FFT and `cols` Z lines through a 1D FFT, scaled
+    to the whole volume."""
+    import scipy.fft as sfft
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(5)
+    a = (rng.random((budget_planes, 1024, 1024), dtype=np.float32) - 0.5).astype(np.complex64)
+    z = (rng.random((cols, 1024), dtype=np.float32) - 0.5).astype(np.complex64)
+    sfft.fft2(a[:2], workers=cores)
+    t0 = time.perf_counter()
+    sfft.fft2(a, workers=cores)
+    t_xy = (time.perf_counter() - t0) * (1024 / budget_planes)
+    t0 = time.perf_counter()
+    sfft.fft(z, axis=1, workers=cores)
+    t_z = (time.perf_counter() - t0) * ((1 << 20) / cols)
+    t = t_xy + t_z
+    flops = 5 * 2 ** 30 * 30
+    return {"value": flops / t / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{budget_planes}/1024 XY planes (fft2) + {cols}/1048576 Z lines (fft) in complex64, "
+                      f"scaled to the full volume; scipy.fft (pocketfft) workers={cores}",
+            "seconds_full_volume_est": t}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-detail", action="store_true", help="skip the four single-GPU configurations")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    peak, peak_src = measured_peak_gbs()
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        t0 = time.perf_counter()
+        vals = []
+        for _ in range(max(1, min(args.steps, 3))):
+            vals.append(cpu_baseline_3d())
+        cb = max(vals, key=lambda v: v["value"])
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["seconds_full_volume_est"] * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": HEADLINE, "n_gpus": args.gpus},
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0, "wall_s": time.perf_counter() - t0}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    import rocfft_b200 as rf
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    if not os.path.exists(rf.LIB_PATH):
+        raise SystemExit(f"{rf.LIB_PATH} missing: run `python -m rocfft_b200.build` first")
+    assert rf.rocfft_setup() == 0
+
+    if world > 1 or args.gpus > 1:
+        from rocfft_b200 import distributed as dist_fft
+        return dist_fft.bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src)
+
+    torch.cuda.set_device(0)
+    W = workloads()
+    with ClockSampler(0) as cs:
+        head = run_single_gpu(HEADLINE, W[HEADLINE], args.steps, args.warmup, peak, do_e2e=False)
+    clocks = cs.summary()
+    if not args.no_e2e:
+        e2e = run_single_gpu(HEADLINE, W[HEADLINE], 2, 1, peak, do_e2e=True, e2e_steps=max(2, min(args.steps, 5)))["e2e"]
+    else:
+        e2e = None
+    detail = []
+    if not args.no_detail:
+        for name in W:
+            if name == HEADLINE:
+                continue
+            r = run_single_gpu(name, W[name], max(args.steps, 10), args.warmup, peak, do_e2e=not args.no_e2e,
+                               e2e_steps=3)
+            detail.append(r)
+
+    dom = max(head["kernels"], key=lambda k: k["ms"])
+    per_launch_bytes = 2 * (1 << 30) * 8  # each pass reads and writes the whole 8 GiB array
+    roof = {"bound": "hbm", "kernel": dom["name"], "achieved": per_launch_bytes / dom["ms"] / 1e6, "peak": peak,
+            "peak_source": peak_src, "unit": "GB/s", "frac": per_launch_bytes / dom["ms"] / 1e6 / peak,
+            "traffic": None, "kernel_ms": dom["ms"],
+            "whole_transform": {"algorithmic_bytes": head["algorithmic_bytes"], "achieved": head["hbm_gbs"],
+                                "frac": head["hbm_frac"]}}
+    line = {"metric": METRIC, "value": head["gflops"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": HEADLINE, "lengths": [1024, 1024, 1024], "batch": 1, "placement": "inplace",
+                       "scale_factor": "1/sqrt(N) (fused, keeps repeated steps finite)",
+                       "l2": "input 8 GiB >> 126 MB L2, no flush needed"},
+            "roofline": roof, "clocks": clocks, "gpu_launches": head["gpu_launches"],
+            "kernels": head["kernels"]}
+    if e2e:
+        line["e2e"] = e2e
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline_3d()
+    if detail:
+        line["configs"] = detail
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -28,6 +28,22 @@ ROCFFT_EXPORT rocfft_status b200fft_stacked_twiddles(
 ROCFFT_EXPORT rocfft_status b200fft_pool_query(
     size_t index, int* length, int* precision, int* variant, int* factors8, size_t* count);
 
+/* Number of GPU kernels this library has launched in the calling process. */
+ROCFFT_EXPORT unsigned long long b200fft_launch_count();
+
+/* Profiling aid in the spirit of the reference's profile log layer
+ * (library/src/powX.cpp:817-883): runs the plan once with a CUDA event between
+ * consecutive kernel launches, synchronises, and writes each step's device time
+ * in milliseconds to step_ms[0 .. *nsteps).  A plan that needs a work buffer
+ * must be given one through `info`. */
+ROCFFT_EXPORT rocfft_status b200fft_execute_profiled(const rocfft_plan     plan,
+                                                     void*                 in_buffer[],
+                                                     void*                 out_buffer[],
+                                                     rocfft_execution_info info,
+                                                     float*                step_ms,
+                                                     size_t                max_steps,
+                                                     size_t*               nsteps);
+
 #ifdef __cplusplus
 }
 #endif

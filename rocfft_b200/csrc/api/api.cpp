@@ -665,6 +665,43 @@ ROCFFT_EXPORT rocfft_status b200fft_plan_describe(const rocfft_plan plan, char* 
     return rocfft_status_success;
 }
 
+ROCFFT_EXPORT unsigned long long b200fft_launch_count()
+{
+    return b200fft::g_launch_count.load();
+}
+
+// Executes the plan once with an event between consecutive steps and reports
+// each step's device time; synchronises the stream (profiling only).
+ROCFFT_EXPORT rocfft_status b200fft_execute_profiled(const rocfft_plan     plan,
+                                                     void*                 in_buffer[],
+                                                     void*                 out_buffer[],
+                                                     rocfft_execution_info info,
+                                                     float*                step_ms,
+                                                     size_t                max_steps,
+                                                     size_t*               nsteps)
+{
+    if(!plan || !plan->core || !in_buffer || !step_ms || !nsteps)
+        return rocfft_status_failure;
+    const b200fft::PlanCore& core = *plan->core;
+    rocfft_execution_info_t  ei;
+    if(info)
+        ei = *info;
+    if(core.work_bytes > 0 && (!ei.workBuffer || ei.workBufferSize < core.work_bytes))
+        return rocfft_status_invalid_work_buffer;
+    const size_t             n = core.steps.size();
+    std::vector<cudaEvent_t> ev(n + 1);
+    for(auto& e : ev)
+        cudaEventCreate(&e);
+    rocfft_status st = b200fft::execute_core(core, in_buffer, out_buffer, ei.workBuffer, ei.stream, ev.data());
+    cudaStreamSynchronize(ei.stream);
+    *nsteps = n;
+    for(size_t i = 0; i < n && i < max_steps; ++i)
+        cudaEventElapsedTime(&step_ms[i], ev[i], ev[i + 1]);
+    for(auto& e : ev)
+        cudaEventDestroy(e);
+    return st;
+}
+
 ROCFFT_EXPORT rocfft_status b200fft_stacked_twiddles(
     int n, const int* factors, int nfactors, int precision, void* out, size_t out_bytes, size_t* needed)
 {

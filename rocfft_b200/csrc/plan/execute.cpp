@@ -5,6 +5,7 @@
 // offsets, launch) and library/src/transform.cpp:361-474 (ExecPlan::ExecuteAsync).
 // Nothing here synchronises: all work is asynchronous on the caller's stream.
 #include "plan.h"
+#include <atomic>
 
 namespace b200fft
 {
@@ -48,16 +49,23 @@ namespace b200fft
 
     }
 
+    std::atomic<unsigned long long> g_launch_count{0};
+
     rocfft_status execute_core(const PlanCore& core,
                                void* const*    in,
                                void* const*    out,
                                void*           work,
-                               cudaStream_t    stream)
+                               cudaStream_t    stream,
+                               cudaEvent_t*    step_events)
     {
         if(core.host_only)
             return rocfft_status_failure; // no CPU fallback exists
+        size_t step_index = 0;
         for(const Step& s : core.steps)
         {
+            if(step_events)
+                cudaEventRecord(step_events[step_index], stream);
+            ++step_index;
             void *ip[2], *op[2];
             if(!resolve(s.in, in, out, work, ip) || !resolve(s.out, in, out, work, op))
                 return rocfft_status_failure;
@@ -97,6 +105,7 @@ namespace b200fft
                 }
                 if(e != cudaSuccess)
                     return rocfft_status_failure;
+                g_launch_count.fetch_add(1, std::memory_order_relaxed);
 
                 size_t k = 0;
                 for(; k < idx.size(); ++k)
@@ -109,6 +118,8 @@ namespace b200fft
                     break;
             }
         }
+        if(step_events)
+            cudaEventRecord(step_events[step_index], stream);
         return rocfft_status_success;
     }
 }

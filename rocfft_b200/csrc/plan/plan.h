@@ -10,6 +10,7 @@
 #include "../launch/launch.h"
 #include "rocfft/rocfft.h"
 #include <cstddef>
+#include <atomic>
 #include <cstdint>
 #include <memory>
 #include <string>
@@ -153,8 +154,10 @@ namespace b200fft
                                void* const*    in,
                                void* const*    out,
                                void*           work,
-                               cudaStream_t    stream);
+                               cudaStream_t    stream,
+                               cudaEvent_t*    step_events = nullptr); // steps+1 events when profiling
     std::string describe_core(const PlanCore& core);
+    extern std::atomic<unsigned long long> g_launch_count; // kernels launched by this library
 
     // host-side table builders (long double internally)
     // `out` receives interleaved (re, im) pairs in the requested precision
