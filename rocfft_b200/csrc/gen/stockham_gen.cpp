@@ -29,7 +29,7 @@
 namespace
 {
     // radices the pass engine may use; each gets a generated butterfly
-    const std::vector<int> kRadices = {2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16};
+    const std::vector<int> kRadices = {2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16, 32};
 
     // lengths with a single-kernel implementation; `small` selects a short
     // list for quick bring-up builds
@@ -204,45 +204,46 @@ int main(int argc, char** argv)
             const int tpt = n / ept;
             for(const Variant& v : kVariants)
             {
-                const bool coop = strcmp(v.cin, "COOP_NONE") || strcmp(v.cout_, "COOP_NONE");
+                // Launch shape.  Measured on B200: many small CTAs per SM overlap their
+                // load / compute / store phases best, so row kernels aim at 128-thread
+                // CTAs and column kernels at 64-byte-wide tiles, and the register cap
+                // is set so that as many CTAs as possible stay resident.
+                const bool coop    = strcmp(v.cin, "COOP_NONE") || strcmp(v.cout_, "COOP_NONE");
+                const int  esz     = prec == 0 ? 8 : 16;
+                const int  npass   = (int)ch.f.size();
+                const int  regcap  = prec == 0 ? (v.col ? 64 : 80) : 128;
+                const int  max_thr = std::min(1024, 65536 / regcap);
                 int        tpb;
                 if(v.col)
                 {
-                    tpb = prec == 0 ? 16 : 8;
-                    while(tpb > 1
-                          && (tpt * tpb > 1024
-                              || smem_bytes(n, tpb, true, prec, coop, (int)ch.f.size()) > smem_cap))
+                    tpb = std::max(64 / esz, std::min(64, 64 / tpt)); // at least 64 threads for short lengths
+                    if(coop)
+                        tpb = std::max(tpb, 128 / esz);
+                    while(tpb > 1 && (tpt * tpb > max_thr || smem_bytes(n, tpb, true, prec, coop, npass) > smem_cap))
                         tpb /= 2;
                     // a column tile narrower than 32 bytes gains nothing over the row kernel
-                    if(tpb * (prec == 0 ? 8 : 16) < 32)
-                        continue;
-                    if(tpt * tpb > 1024)
+                    if(tpb * esz < 32 || tpt * tpb > 1024)
                         continue;
                 }
                 else
                 {
-                    int target = coop ? 256 : 256;
-                    tpb        = std::max(1, std::min(64, target / tpt));
+                    tpb = std::max(1, std::min(64, 128 / tpt));
                     if(coop)
-                        tpb = std::max(tpb, prec == 0 ? 16 : 8); // transposed stores need a wide tile
-                    while(tpb > 1
-                          && (tpt * tpb > 1024
-                              || smem_bytes(n, tpb, false, prec, coop, (int)ch.f.size()) > smem_cap))
+                        tpb = std::max(tpb, 128 / esz); // transposed stores need a wide tile
+                    while(tpb > 1 && (tpt * tpb > max_thr || smem_bytes(n, tpb, false, prec, coop, npass) > smem_cap))
                         tpb /= 2;
                     if(tpt * tpb > 1024)
                         continue;
-                    if(coop && tpb * (prec == 0 ? 8 : 16) < 32)
+                    if(coop && tpb * esz < 32)
                         continue;
                 }
-                size_t sm = smem_bytes(n, tpb, v.col, prec, coop, (int)ch.f.size());
+                size_t sm = smem_bytes(n, tpb, v.col, prec, coop, npass);
                 if(sm > smem_cap)
                     continue;
                 const int threads = tpt * tpb;
-                // register budget: data + twiddles + temporaries
-                const int regs_est = (prec == 0 ? 3 : 6) * ept + 40;
-                int       minb     = std::max(1, 65536 / (threads * std::min(regs_est, 255)));
+                int       minb    = std::max(1, 65536 / (threads * regcap));
                 if(sm)
-                    minb = std::min<int>(minb, (int)(220 * 1024 / (sm + 1024)));
+                    minb = std::min<int>(minb, (int)(200 * 1024 / (sm + 1024)));
                 minb = std::max(1, std::min(minb, 2048 / threads));
                 minb = std::min(minb, 8);
 
