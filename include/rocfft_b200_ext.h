@@ -28,6 +28,18 @@ ROCFFT_EXPORT rocfft_status b200fft_stacked_twiddles(
 ROCFFT_EXPORT rocfft_status b200fft_pool_query(
     size_t index, int* length, int* precision, int* variant, int* factors8, size_t* count);
 
+/* NCCL communicator helpers for multi-process plans (one process per GPU).
+ * The reference takes an MPI communicator through
+ * rocfft_plan_description_set_comm(desc, rocfft_comm_mpi, &comm)
+ * (library/src/plan.cpp:356-395); this library takes
+ * rocfft_comm_nccl with a pointer to an ncclComm_t.  These three calls let a
+ * program that does not link NCCL itself build one: rank 0 creates the
+ * 128-byte id, the program ships it to the other ranks by any means, and every
+ * rank creates its communicator (collective call). */
+ROCFFT_EXPORT rocfft_status b200fft_nccl_unique_id(void* id128);
+ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_create(int nranks, int rank, const void* id128, void** comm);
+ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_destroy(void* comm);
+
 /* Number of GPU kernels this library has launched in the calling process. */
 ROCFFT_EXPORT unsigned long long b200fft_launch_count();
 

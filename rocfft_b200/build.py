@@ -126,7 +126,7 @@ def build(small: bool = False, jobs: int | None = None, force: bool = False, ver
     need_link = bool(tasks) or not os.path.exists(LIB)
     if need_link:
         cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
-                                                      "-Xlinker", "--no-undefined"]
+                                                      "-Xlinker", "--no-undefined", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stderr[-4000:])

@@ -665,6 +665,21 @@ ROCFFT_EXPORT rocfft_status b200fft_plan_describe(const rocfft_plan plan, char* 
     return rocfft_status_success;
 }
 
+ROCFFT_EXPORT rocfft_status b200fft_nccl_unique_id(void* id128)
+{
+    return b200fft::nccl_unique_id(id128) == 0 ? rocfft_status_success : rocfft_status_failure;
+}
+ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_create(int nranks, int rank, const void* id128, void** comm)
+{
+    if(!id128 || !comm)
+        return rocfft_status_invalid_arg_value;
+    return b200fft::nccl_comm_create(nranks, rank, id128, comm) == 0 ? rocfft_status_success : rocfft_status_failure;
+}
+ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_destroy(void* comm)
+{
+    return b200fft::nccl_comm_destroy(comm) == 0 ? rocfft_status_success : rocfft_status_failure;
+}
+
 ROCFFT_EXPORT unsigned long long b200fft_launch_count()
 {
     return b200fft::g_launch_count.load();

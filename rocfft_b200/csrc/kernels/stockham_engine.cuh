@@ -120,6 +120,18 @@ namespace b200fft
     // ------------------------------------------------------------------
     // global-memory element access
     // ------------------------------------------------------------------
+    // offset of point e of a transform along its (possibly two-level) stride
+    __device__ __forceinline__ long long elem_offset(const b200fft_ioview& v, int e)
+    {
+        if(v.blk)
+        {
+            const unsigned q = __umulhi((unsigned)e, v.blk_mul);
+            const unsigned r = (unsigned)e - q * v.blk;
+            return (long long)q * v.bs + (long long)r * v.es;
+        }
+        return (long long)e * v.es;
+    }
+
     template <class C>
     __device__ __forceinline__ typename C::T2
         gload(const b200fft_ioview& v, long long base, int e, bool inverse)
@@ -133,11 +145,11 @@ namespace b200fft
         }
         else if constexpr(C::IOK == IO_STRIDED)
         {
-            r = reinterpret_cast<const T2*>(v.p[0])[base + (long long)e * v.es];
+            r = reinterpret_cast<const T2*>(v.p[0])[base + elem_offset(v, e)];
         }
         else
         {
-            const long long off = base + (long long)e * v.es;
+            const long long off = base + elem_offset(v, e);
             if(v.planar)
             {
                 r.x = reinterpret_cast<const T*>(v.p[0])[off];
@@ -173,11 +185,11 @@ namespace b200fft
         }
         else if constexpr(C::IOK == IO_STRIDED)
         {
-            reinterpret_cast<T2*>(v.p[0])[base + (long long)e * v.es] = val;
+            reinterpret_cast<T2*>(v.p[0])[base + elem_offset(v, e)] = val;
         }
         else
         {
-            const long long off = base + (long long)e * v.es;
+            const long long off = base + elem_offset(v, e);
             if(v.planar)
             {
                 reinterpret_cast<T*>(v.p[0])[off] = val.x;

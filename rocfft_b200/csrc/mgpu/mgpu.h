@@ -19,4 +19,9 @@ namespace b200fft
                                             void* const*                   in,
                                             void* const*                   out,
                                             const rocfft_execution_info_t* info);
+
+    // NCCL communicator helpers (0 on success)
+    int nccl_unique_id(void* out128);
+    int nccl_comm_create(int nranks, int rank, const void* id128, void** comm_out);
+    int nccl_comm_destroy(void* comm);
 }

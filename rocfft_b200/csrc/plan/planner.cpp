@@ -21,7 +21,7 @@
 //     (reference: tree_node_bluestein.cpp:63-408).
 // Real transforms wrap a half-length complex stage in pre/post-processing
 // (reference: tree_node_real.cpp:211-449).
-#include "plan.h"
+#include "planner_impl.h"
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -43,906 +43,9 @@ namespace b200fft
             cudaSetDevice(prev);
     }
 
+    using namespace detail;
     namespace
     {
-        struct OuterDim
-        {
-            size_t    len;
-            ptrdiff_t is, os;
-        };
-
-        struct Stage
-        {
-            size_t                n = 1;
-            ptrdiff_t             is = 1, os = 1;
-            std::vector<OuterDim> outer;
-            BufRef                in, out;
-            bool                  inverse   = false;
-            bool                  use_scale = false;
-            double                scale     = 1.0;
-        };
-
-        const b200fft_pool_entry* pool_find(size_t n, int prec, int variant)
-        {
-            static std::map<std::tuple<size_t, int, int>, const b200fft_pool_entry*> index;
-            static bool                                                            built = false;
-            if(!built)
-            {
-                size_t                    cnt = 0;
-                const b200fft_pool_entry* p   = b200fft_pool(&cnt);
-                for(size_t i = 0; i < cnt; ++i)
-                    index[{(size_t)p[i].length, p[i].precision, p[i].variant}] = &p[i];
-                built = true;
-            }
-            auto it = index.find({n, prec, variant});
-            return it == index.end() ? nullptr : it->second;
-        }
-
-        bool pool_has(size_t n, int prec)
-        {
-            return pool_find(n, prec, B200FFT_ROW_GEN) != nullptr;
-        }
-
-        size_t largest_pool_length(int prec)
-        {
-            static size_t best[2] = {0, 0};
-            if(!best[prec])
-            {
-                size_t                    cnt = 0;
-                const b200fft_pool_entry* p   = b200fft_pool(&cnt);
-                for(size_t i = 0; i < cnt; ++i)
-                    if(p[i].precision == prec)
-                        best[prec] = std::max(best[prec], (size_t)p[i].length);
-            }
-            return best[prec];
-        }
-
-        class Planner
-        {
-        public:
-            Planner(PlanCore& core)
-                : core_(core)
-                , prec_(core.precision)
-                , rsize_(core.precision == 0 ? 4 : 8)
-                , csize_(core.precision == 0 ? 8 : 16)
-            {
-            }
-
-            // ---------------- temp arena ----------------
-            size_t temp_alloc(size_t bytes)
-            {
-                size_t off = (temp_cur_ + 255) & ~size_t(255);
-                temp_cur_  = off + bytes;
-                core_.work_bytes = std::max(core_.work_bytes, temp_cur_);
-                return off;
-            }
-            size_t temp_mark() const
-            {
-                return temp_cur_;
-            }
-            void temp_release(size_t mark)
-            {
-                temp_cur_ = mark;
-            }
-
-            // ---------------- device tables ----------------
-            const void* upload(const std::vector<char>& host)
-            {
-                void* d = nullptr;
-                if(core_.host_only)
-                    return nullptr;
-                cudaError_t e = cudaMalloc(&d, std::max<size_t>(host.size(), 16));
-                if(e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver)
-                {
-                    // no GPU in this process: the plan can still be built and
-                    // inspected (work-buffer size, step list) but not executed
-                    cudaGetLastError();
-                    core_.host_only = true;
-                    return nullptr;
-                }
-                if(e != cudaSuccess)
-                    throw std::runtime_error("device table allocation failed");
-                core_.tables.push_back(d);
-                if(cudaMemcpy(d, host.data(), host.size(), cudaMemcpyHostToDevice) != cudaSuccess)
-                    throw std::runtime_error("device table upload failed");
-                return d;
-            }
-            const void* stacked_twiddles(const b200fft_pool_entry* k)
-            {
-                auto key = std::make_pair(k->length, std::vector<int>(k->factors, k->factors + k->nfactors));
-                auto it  = tw_cache_.find(key);
-                if(it != tw_cache_.end())
-                    return it->second;
-                std::vector<char> h;
-                host_stacked_twiddles(k->length, k->factors, k->nfactors, prec_, h);
-                const void* d  = upload(h);
-                tw_cache_[key] = d;
-                return d;
-            }
-
-            // ---------------- 1D complex stage ----------------
-            bool can_plan_smooth(size_t n) const
-            {
-                if(n == 1 || pool_has(n, prec_))
-                    return true;
-                size_t n1, n2;
-                return choose_split(n, n1, n2);
-            }
-
-            // n = n1 * n2 with n1 in the pool and n2 plannable; as balanced as possible
-            bool choose_split(size_t n, size_t& n1, size_t& n2) const
-            {
-                const size_t lim  = largest_pool_length(prec_);
-                bool         found = false;
-                double       best  = 0;
-                for(size_t d = 2; d <= lim && d * d <= n * lim; ++d)
-                {
-                    if(n % d || !pool_has(d, prec_))
-                        continue;
-                    const size_t e = n / d;
-                    if(e < 2)
-                        continue;
-                    bool ok = pool_has(e, prec_);
-                    if(!ok && e > lim)
-                    {
-                        size_t a, b;
-                        ok = choose_split(e, a, b);
-                    }
-                    if(!ok)
-                        continue;
-                    // balance score: closer to sqrt(n) is better; the column pass
-                    // prefers the smaller factor
-                    double score = -std::fabs(std::log((double)d) - 0.5 * std::log((double)n));
-                    if(d > e)
-                        score -= 1e-3;
-                    if(!found || score > best)
-                    {
-                        found = true;
-                        best  = score;
-                        n1    = d;
-                        n2    = e;
-                    }
-                }
-                return found;
-            }
-
-            size_t choose_bluestein_length(size_t n) const
-            {
-                const size_t lo = 2 * n - 1;
-                size_t       p2 = 1;
-                while(p2 < lo)
-                    p2 <<= 1;
-                for(size_t m = lo; m < p2; ++m)
-                {
-                    size_t r = m;
-                    for(size_t q : {2, 3, 5, 7})
-                        while(r % q == 0)
-                            r /= q;
-                    if(r != 1)
-                        continue;
-                    // a non-power-of-two length must save enough to be worth it
-                    if((double)m > 0.9 * (double)p2)
-                        break;
-                    if(can_plan_smooth(m))
-                        return m;
-                }
-                if(!can_plan_smooth(p2))
-                    throw std::runtime_error("no Bluestein length available");
-                return p2;
-            }
-
-            static void drop_unit_dims(std::vector<OuterDim>& o)
-            {
-                o.erase(std::remove_if(o.begin(), o.end(), [](const OuterDim& d) { return d.len == 1; }),
-                        o.end());
-            }
-
-            // merge outer dims that are contiguous continuations of each other on both sides
-            static void merge_dims(std::vector<OuterDim>& o)
-            {
-                bool again = true;
-                while(again)
-                {
-                    again = false;
-                    for(size_t a = 0; a < o.size() && !again; ++a)
-                        for(size_t b = 0; b < o.size() && !again; ++b)
-                        {
-                            if(a == b)
-                                continue;
-                            if((ptrdiff_t)o[a].len * o[a].is == o[b].is
-                               && (ptrdiff_t)o[a].len * o[a].os == o[b].os
-                               && o[a].len * o[b].len < 0x7fffffffull)
-                            {
-                                o[a].len *= o[b].len;
-                                o.erase(o.begin() + b);
-                                again = true;
-                            }
-                        }
-                }
-            }
-
-            // fills on[]/os[] of a kernel argument block from an ordered outer list;
-            // dimensions beyond three become host loops
-            template <class ARGS>
-            static void fill_outer(const std::vector<OuterDim>& o, ARGS& a, std::vector<LoopDim>& loops)
-            {
-                for(int k = 0; k < 3; ++k)
-                {
-                    a.on[k]     = 1;
-                    a.in.os[k]  = 0;
-                    a.out.os[k] = 0;
-                }
-                for(size_t k = 0; k < o.size(); ++k)
-                {
-                    if(o[k].len > 0xffffffffull)
-                        throw std::runtime_error("dimension too long");
-                    if(k < 3)
-                    {
-                        a.on[k]     = (unsigned)o[k].len;
-                        a.in.os[k]  = o[k].is;
-                        a.out.os[k] = o[k].os;
-                    }
-                    else
-                        loops.push_back({o[k].len, o[k].is, o[k].os});
-                }
-            }
-
-            size_t elem_bytes(const BufRef& b) const
-            {
-                return b.planar ? rsize_ : csize_;
-            }
-
-            void emit_copy(const Stage& s)
-            {
-                Step st;
-                st.kind    = Step::EW;
-                st.ew_kind = B200FFT_EW_COPY_C2C;
-                st.in      = s.in;
-                st.out     = s.out;
-                st.ea.n    = (unsigned)s.n;
-                st.ea.in.es = s.is;
-                st.ea.out.es = s.os;
-                st.ea.in.planar = s.in.planar;
-                st.ea.out.planar = s.out.planar;
-                st.ea.use_scale = s.use_scale;
-                st.ea.scale     = s.scale;
-                std::vector<OuterDim> o = s.outer;
-                drop_unit_dims(o);
-                fill_outer(o, st.ea, st.loops);
-                st.in_elem_bytes  = elem_bytes(s.in);
-                st.out_elem_bytes = elem_bytes(s.out);
-                st.note           = "copy";
-                core_.steps.push_back(st);
-            }
-
-            void emit_c2c_1d(Stage s)
-            {
-                drop_unit_dims(s.outer);
-                for(const auto& d : s.outer)
-                    if(d.len == 0)
-                        return;
-                if(s.n == 1)
-                {
-                    const bool same = s.in.id == s.out.id && s.in.byte_off[0] == s.out.byte_off[0]
-                                      && s.in.byte_off[1] == s.out.byte_off[1] && s.in.planar == s.out.planar;
-                    bool same_strides = true;
-                    for(const auto& d : s.outer)
-                        same_strides = same_strides && d.is == d.os;
-                    if(same && same_strides && !s.use_scale)
-                        return;
-                    emit_copy(s);
-                    return;
-                }
-                if(pool_has(s.n, prec_))
-                {
-                    emit_tile(s);
-                    return;
-                }
-                size_t n1, n2;
-                bool   smooth = true;
-                {
-                    size_t r = s.n;
-                    for(size_t q : {2, 3, 5, 7, 11, 13})
-                        while(r % q == 0)
-                            r /= q;
-                    smooth = (r == 1);
-                }
-                if(smooth && choose_split(s.n, n1, n2))
-                {
-                    emit_large(s, n1, n2);
-                    return;
-                }
-                emit_bluestein(s);
-            }
-
-            void emit_tile(const Stage& s)
-            {
-                const bool il = !s.in.planar && !s.out.planar;
-                std::vector<OuterDim> o = s.outer;
-                merge_dims(o);
-
-                auto find_dim = [&](bool need_is1, bool need_os1) -> int {
-                    int best = -1;
-                    for(size_t k = 0; k < o.size(); ++k)
-                    {
-                        if(need_is1 && o[k].is != 1)
-                            continue;
-                        if(need_os1 && o[k].os != 1)
-                            continue;
-                        if(o[k].len < 2)
-                            continue;
-                        if(best < 0 || o[k].len > o[best].len)
-                            best = (int)k;
-                    }
-                    return best;
-                };
-
-                const b200fft_pool_entry* kern    = nullptr;
-                int                       tiledim = -1;
-                if(s.is == 1 && s.os == 1)
-                {
-                    kern = pool_find(s.n, prec_, il ? B200FFT_ROW_UNIT : B200FFT_ROW_GEN);
-                }
-                else
-                {
-                    int k;
-                    if((k = find_dim(true, true)) >= 0
-                       && (kern = pool_find(s.n, prec_, il ? B200FFT_COL_STR : B200FFT_COL_GEN)))
-                        tiledim = k;
-                    else if(il && s.is == 1 && (k = find_dim(false, true)) >= 0
-                            && (kern = pool_find(s.n, prec_, B200FFT_ROW_TOUT)))
-                        tiledim = k;
-                    else if(il && s.os == 1 && (k = find_dim(true, false)) >= 0
-                            && (kern = pool_find(s.n, prec_, B200FFT_COL_ROUT)))
-                        tiledim = k;
-                    else
-                        kern = nullptr;
-                }
-                if(!kern)
-                    kern = pool_find(s.n, prec_, B200FFT_ROW_GEN);
-                if(!kern)
-                    throw std::runtime_error("no kernel for length");
-
-                // order outer dims: the tiled one first, the rest by input stride
-                if(tiledim < 0 && !o.empty())
-                {
-                    tiledim = 0;
-                    for(size_t k = 1; k < o.size(); ++k)
-                        if(std::llabs((long long)o[k].is) < std::llabs((long long)o[tiledim].is))
-                            tiledim = (int)k;
-                }
-                if(tiledim > 0)
-                    std::swap(o[0], o[tiledim]);
-                if(o.size() > 2)
-                    std::sort(o.begin() + 1, o.end(), [](const OuterDim& a, const OuterDim& b) {
-                        return a.is < b.is;
-                    });
-
-                Step st;
-                st.kind = Step::TILE;
-                st.kern = kern;
-                st.in   = s.in;
-                st.out  = s.out;
-                b200fft_kargs& a = st.ka;
-                a.in.es      = s.is;
-                a.out.es     = s.os;
-                a.in.planar  = s.in.planar;
-                a.out.planar = s.out.planar;
-                fill_outer(o, a, st.loops);
-                a.ntile0    = (a.on[0] + kern->tpb - 1) / kern->tpb;
-                a.inverse   = s.inverse;
-                a.use_scale = s.use_scale;
-                a.scale     = s.scale;
-                a.twiddles  = stacked_twiddles(kern);
-                st.ntiles   = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];
-                st.in_elem_bytes  = elem_bytes(s.in);
-                st.out_elem_bytes = elem_bytes(s.out);
-                st.note           = kern->name;
-                core_.steps.push_back(st);
-            }
-
-            // total number of transforms and contiguous strides for a temp laid out
-            // [outer (in the order given, first fastest)][row]
-            static size_t temp_outer_strides(const std::vector<OuterDim>& o, size_t row, std::vector<ptrdiff_t>& ts)
-            {
-                size_t cum = row;
-                ts.clear();
-                for(const auto& d : o)
-                {
-                    ts.push_back((ptrdiff_t)cum);
-                    cum *= d.len;
-                }
-                return cum; // elements in the whole temp
-            }
-
-            void emit_large(const Stage& s, size_t n1, size_t n2)
-            {
-                const size_t           mark = temp_mark();
-                std::vector<ptrdiff_t> ts;
-                const size_t           total = temp_outer_strides(s.outer, s.n, ts);
-                BufRef                 T;
-                T.id          = BUF_TEMP;
-                T.byte_off[0] = temp_alloc(total * csize_);
-                T.planar      = false;
-
-                // stage A: length n1 along i1 (stride n2), columns i2 adjacent
-                Stage A;
-                A.n  = n1;
-                A.is = (ptrdiff_t)n2 * s.is;
-                A.os = (ptrdiff_t)n2;
-                A.outer.push_back({n2, s.is, 1});
-                for(size_t k = 0; k < s.outer.size(); ++k)
-                    A.outer.push_back({s.outer[k].len, s.outer[k].is, ts[k]});
-                A.in      = s.in;
-                A.out     = T;
-                A.inverse = s.inverse;
-                emit_c2c_1d(A);
-
-                // twiddle multiply W_n^(k1*i2) in place on the temp
-                {
-                    int               steps = 1;
-                    std::vector<char> h;
-                    host_large_twiddles(s.n, prec_, &steps, h);
-                    Step st;
-                    st.kind       = Step::EW;
-                    st.ew_kind    = B200FFT_EW_LARGE_TWIDDLE;
-                    st.in         = T;
-                    st.out        = T;
-                    st.ea.n       = (unsigned)s.n;
-                    st.ea.in.es   = 1;
-                    st.ea.out.es  = 1;
-                    st.ea.inverse = s.inverse;
-                    st.ea.aux[0]  = upload(h);
-                    st.ea.iaux[0] = (long long)n2;
-                    st.ea.iaux[1] = steps;
-                    std::vector<OuterDim> o;
-                    for(size_t k = 0; k < s.outer.size(); ++k)
-                        o.push_back({s.outer[k].len, ts[k], ts[k]});
-                    merge_dims(o);
-                    fill_outer(o, st.ea, st.loops);
-                    st.in_elem_bytes = st.out_elem_bytes = csize_;
-                    st.note                              = "large_twiddle_mul";
-                    core_.steps.push_back(st);
-                }
-
-                // stage B: length n2 along i2 (contiguous), output index k1 + n1*k2
-                Stage B;
-                B.n  = n2;
-                B.is = 1;
-                B.os = (ptrdiff_t)n1 * s.os;
-                B.outer.push_back({n1, (ptrdiff_t)n2, s.os});
-                for(size_t k = 0; k < s.outer.size(); ++k)
-                    B.outer.push_back({s.outer[k].len, ts[k], s.outer[k].os});
-                B.in        = T;
-                B.out       = s.out;
-                B.inverse   = s.inverse;
-                B.use_scale = s.use_scale;
-                B.scale     = s.scale;
-                emit_c2c_1d(B);
-                temp_release(mark);
-            }
-
-            void emit_bluestein(const Stage& s)
-            {
-                const size_t           m    = choose_bluestein_length(s.n);
-                const size_t           mark = temp_mark();
-                std::vector<ptrdiff_t> ts;
-                const size_t           total = temp_outer_strides(s.outer, m, ts);
-                BufRef                 A;
-                A.id          = BUF_TEMP;
-                A.byte_off[0] = temp_alloc(total * csize_);
-
-                std::vector<char> h;
-                host_chirp(s.n, prec_, h);
-                const void* chirp = upload(h);
-                host_bluestein_filter(s.n, m, prec_, h);
-                const void* filt = upload(h);
-
-                {
-                    Step st;
-                    st.kind          = Step::EW;
-                    st.ew_kind       = B200FFT_EW_BLUE_PAD_MUL;
-                    st.in            = s.in;
-                    st.out           = A;
-                    st.ea.n          = (unsigned)s.n;
-                    st.ea.in.es      = s.is;
-                    st.ea.out.es     = 1;
-                    st.ea.in.planar  = s.in.planar;
-                    st.ea.inverse    = s.inverse;
-                    st.ea.aux[0]     = chirp;
-                    st.ea.iaux[0]    = (long long)m;
-                    std::vector<OuterDim> o;
-                    for(size_t k = 0; k < s.outer.size(); ++k)
-                        o.push_back({s.outer[k].len, s.outer[k].is, ts[k]});
-                    fill_outer(o, st.ea, st.loops);
-                    st.in_elem_bytes  = elem_bytes(s.in);
-                    st.out_elem_bytes = csize_;
-                    st.note           = "bluestein_pad_mul";
-                    core_.steps.push_back(st);
-                }
-                const size_t rows = total / m;
-                Stage        F;
-                F.n  = m;
-                F.is = F.os = 1;
-                F.outer.push_back({rows, (ptrdiff_t)m, (ptrdiff_t)m});
-                F.in = F.out = A;
-                emit_c2c_1d(F);
-                {
-                    Step st;
-                    st.kind       = Step::EW;
-                    st.ew_kind    = B200FFT_EW_POINT_MUL;
-                    st.in         = A;
-                    st.out        = A;
-                    st.ea.n       = (unsigned)m;
-                    st.ea.in.es   = 1;
-                    st.ea.out.es  = 1;
-                    st.ea.aux[0]  = filt;
-                    std::vector<OuterDim> o{{rows, (ptrdiff_t)m, (ptrdiff_t)m}};
-                    fill_outer(o, st.ea, st.loops);
-                    st.in_elem_bytes = st.out_elem_bytes = csize_;
-                    st.note                              = "bluestein_filter_mul";
-                    core_.steps.push_back(st);
-                }
-                F.inverse = true;
-                emit_c2c_1d(F);
-                {
-                    Step st;
-                    st.kind          = Step::EW;
-                    st.ew_kind       = B200FFT_EW_BLUE_RES_MUL;
-                    st.in            = A;
-                    st.out           = s.out;
-                    st.ea.n          = (unsigned)s.n;
-                    st.ea.in.es      = 1;
-                    st.ea.out.es     = s.os;
-                    st.ea.out.planar = s.out.planar;
-                    st.ea.inverse    = s.inverse;
-                    st.ea.use_scale  = s.use_scale;
-                    st.ea.scale      = s.scale;
-                    st.ea.aux[0]     = chirp;
-                    std::vector<OuterDim> o;
-                    for(size_t k = 0; k < s.outer.size(); ++k)
-                        o.push_back({s.outer[k].len, ts[k], s.outer[k].os});
-                    fill_outer(o, st.ea, st.loops);
-                    st.in_elem_bytes  = csize_;
-                    st.out_elem_bytes = elem_bytes(s.out);
-                    st.note           = "bluestein_res_mul";
-                    core_.steps.push_back(st);
-                }
-                temp_release(mark);
-            }
-
-            // ---------------- whole-transform drivers ----------------
-            static std::vector<OuterDim> outer_of(const DataView& in, const DataView& out, int skip)
-            {
-                std::vector<OuterDim> o;
-                for(size_t k = 0; k < in.len.size(); ++k)
-                    if((int)k != skip)
-                        o.push_back({out.len[k], in.stride[k], out.stride[k]});
-                o.push_back({in.batch, in.dist, out.dist});
-                return o;
-            }
-
-            void plan_c2c(const DataView& in, const DataView& out, bool inverse, double scale, bool inplace_alias)
-            {
-                const size_t rank      = in.len.size();
-                const bool   use_scale = scale != 1.0;
-                // an in-place transform whose input and output layouts differ cannot
-                // run stage by stage in the user's buffer: go through a scratch copy
-                bool layouts_equal = in.dist == out.dist && in.stride == out.stride
-                                     && in.buf.byte_off[0] == out.buf.byte_off[0]
-                                     && in.buf.byte_off[1] == out.buf.byte_off[1];
-                if(inplace_alias && !layouts_equal)
-                {
-                    DataView t = in;
-                    t.kind     = EK_CPLX_IL;
-                    t.buf      = BufRef();
-                    t.buf.id   = BUF_TEMP;
-                    size_t cum = 1;
-                    for(size_t k = 0; k < rank; ++k)
-                    {
-                        t.stride[k] = (ptrdiff_t)cum;
-                        cum *= in.len[k];
-                    }
-                    t.dist            = (ptrdiff_t)cum;
-                    t.buf.byte_off[0] = temp_alloc(cum * in.batch * csize_);
-                    plan_c2c(in, t, inverse, 1.0, false);
-                    Stage c;
-                    c.n     = in.len[0];
-                    c.is    = t.stride[0];
-                    c.os    = out.stride[0];
-                    c.outer = outer_of(t, out, 0);
-                    c.in    = t.buf;
-                    c.out   = out.buf;
-                    c.use_scale = use_scale;
-                    c.scale     = scale;
-                    emit_copy(c);
-                    return;
-                }
-                for(size_t d = 0; d < rank; ++d)
-                {
-                    const DataView& src = (d == 0) ? in : out;
-                    Stage           s;
-                    s.n       = in.len[d];
-                    s.is      = src.stride[d];
-                    s.os      = out.stride[d];
-                    s.outer   = outer_of(src, out, (int)d);
-                    s.in      = src.buf;
-                    s.out     = out.buf;
-                    s.inverse = inverse;
-                    if(d == rank - 1 && use_scale)
-                    {
-                        s.use_scale = true;
-                        s.scale     = scale;
-                    }
-                    emit_c2c_1d(s);
-                }
-            }
-
-            // real forward along dimension 0: `in` real view, `out` Hermitian view
-            void plan_r2c_dim0(const DataView& in, const DataView& out, bool use_scale, double scale)
-            {
-                const size_t n0   = in.len[0];
-                const size_t mark = temp_mark();
-                bool         even_ok = (n0 % 2 == 0) && n0 >= 2 && in.stride[0] == 1 && (in.dist % 2 == 0)
-                               && (in.buf.byte_off[0] % csize_ == 0);
-                for(size_t k = 1; k < in.len.size(); ++k)
-                    even_ok = even_ok && (in.stride[k] % 2 == 0);
-                std::vector<OuterDim> o_in = outer_of(in, out, 0); // (len, real strides, herm strides)
-                // lengths of outer dims are the same on both sides
-                std::vector<ptrdiff_t> ts;
-                if(even_ok)
-                {
-                    const size_t h     = n0 / 2;
-                    const size_t total = temp_outer_strides(o_in, h, ts);
-                    BufRef       Z;
-                    Z.id          = BUF_TEMP;
-                    Z.byte_off[0] = temp_alloc(total * csize_);
-                    Stage s;
-                    s.n  = h;
-                    s.is = 1;
-                    s.os = 1;
-                    for(size_t k = 0; k < o_in.size(); ++k)
-                        s.outer.push_back({o_in[k].len, o_in[k].is / 2, ts[k]});
-                    s.in        = in.buf; // real pairs read as complex
-                    s.in.planar = false;
-                    s.out       = Z;
-                    emit_c2c_1d(s);
-
-                    std::vector<char> hbuf;
-                    host_half_twiddles(n0, prec_, hbuf);
-                    Step st;
-                    st.kind          = Step::EW;
-                    st.ew_kind       = B200FFT_EW_R2C_POST;
-                    st.in            = Z;
-                    st.out           = out.buf;
-                    st.ea.n          = (unsigned)h;
-                    st.ea.in.es      = 1;
-                    st.ea.out.es     = out.stride[0];
-                    st.ea.out.planar = out.buf.planar;
-                    st.ea.use_scale  = use_scale;
-                    st.ea.scale      = scale;
-                    st.ea.aux[0]     = upload(hbuf);
-                    std::vector<OuterDim> o;
-                    for(size_t k = 0; k < o_in.size(); ++k)
-                        o.push_back({o_in[k].len, ts[k], o_in[k].os});
-                    drop_unit_dims(o);
-                    fill_outer(o, st.ea, st.loops);
-                    st.in_elem_bytes  = csize_;
-                    st.out_elem_bytes = elem_bytes(out.buf);
-                    st.note           = "r2c_even_post";
-                    core_.steps.push_back(st);
-                }
-                else
-                {
-                    const size_t total = temp_outer_strides(o_in, n0, ts);
-                    BufRef       C;
-                    C.id          = BUF_TEMP;
-                    C.byte_off[0] = temp_alloc(total * csize_);
-                    {
-                        Step st;
-                        st.kind      = Step::EW;
-                        st.ew_kind   = B200FFT_EW_R2C_COPY;
-                        st.in        = in.buf;
-                        st.out       = C;
-                        st.ea.n      = (unsigned)n0;
-                        st.ea.in.es  = in.stride[0];
-                        st.ea.out.es = 1;
-                        std::vector<OuterDim> o;
-                        for(size_t k = 0; k < o_in.size(); ++k)
-                            o.push_back({o_in[k].len, o_in[k].is, ts[k]});
-                        drop_unit_dims(o);
-                        fill_outer(o, st.ea, st.loops);
-                        st.in_elem_bytes  = rsize_;
-                        st.out_elem_bytes = csize_;
-                        st.note           = "r2c_copy";
-                        core_.steps.push_back(st);
-                    }
-                    Stage s;
-                    s.n  = n0;
-                    s.is = s.os = 1;
-                    s.outer.push_back({total / n0, (ptrdiff_t)n0, (ptrdiff_t)n0});
-                    s.in = s.out = C;
-                    emit_c2c_1d(s);
-                    Stage c;
-                    c.n  = n0 / 2 + 1;
-                    c.is = 1;
-                    c.os = out.stride[0];
-                    for(size_t k = 0; k < o_in.size(); ++k)
-                        c.outer.push_back({o_in[k].len, ts[k], o_in[k].os});
-                    c.in        = C;
-                    c.out       = out.buf;
-                    c.use_scale = use_scale;
-                    c.scale     = scale;
-                    emit_copy(c);
-                }
-                temp_release(mark);
-            }
-
-            // real inverse along dimension 0: `in` Hermitian view, `out` real view
-            void plan_c2r_dim0(const DataView& in, const DataView& out, bool use_scale, double scale)
-            {
-                const size_t n0   = out.len[0];
-                const size_t mark = temp_mark();
-                bool         even_ok = (n0 % 2 == 0) && n0 >= 2 && out.stride[0] == 1 && (out.dist % 2 == 0)
-                               && (out.buf.byte_off[0] % csize_ == 0);
-                for(size_t k = 1; k < out.len.size(); ++k)
-                    even_ok = even_ok && (out.stride[k] % 2 == 0);
-                // outer dims: lengths from the real side (same as Hermitian side for dims >= 1)
-                std::vector<OuterDim> o_io;
-                for(size_t k = 1; k < out.len.size(); ++k)
-                    o_io.push_back({out.len[k], in.stride[k], out.stride[k]});
-                o_io.push_back({in.batch, in.dist, out.dist});
-                std::vector<ptrdiff_t> ts;
-                if(even_ok)
-                {
-                    const size_t h     = n0 / 2;
-                    const size_t total = temp_outer_strides(o_io, h, ts);
-                    BufRef       Z;
-                    Z.id          = BUF_TEMP;
-                    Z.byte_off[0] = temp_alloc(total * csize_);
-                    std::vector<char> hbuf;
-                    host_half_twiddles(n0, prec_, hbuf);
-                    Step st;
-                    st.kind         = Step::EW;
-                    st.ew_kind      = B200FFT_EW_C2R_PRE;
-                    st.in           = in.buf;
-                    st.out          = Z;
-                    st.ea.n         = (unsigned)h;
-                    st.ea.in.es     = in.stride[0];
-                    st.ea.in.planar = in.buf.planar;
-                    st.ea.out.es    = 1;
-                    st.ea.aux[0]    = upload(hbuf);
-                    std::vector<OuterDim> o;
-                    for(size_t k = 0; k < o_io.size(); ++k)
-                        o.push_back({o_io[k].len, o_io[k].is, ts[k]});
-                    drop_unit_dims(o);
-                    fill_outer(o, st.ea, st.loops);
-                    st.in_elem_bytes  = elem_bytes(in.buf);
-                    st.out_elem_bytes = csize_;
-                    st.note           = "c2r_even_pre";
-                    core_.steps.push_back(st);
-
-                    Stage s;
-                    s.n  = h;
-                    s.is = s.os = 1;
-                    for(size_t k = 0; k < o_io.size(); ++k)
-                        s.outer.push_back({o_io[k].len, ts[k], o_io[k].os / 2});
-                    s.in         = Z;
-                    s.out        = out.buf; // real pairs written as complex
-                    s.out.planar = false;
-                    s.inverse    = true;
-                    s.use_scale  = use_scale;
-                    s.scale      = scale;
-                    emit_c2c_1d(s);
-                }
-                else
-                {
-                    const size_t total = temp_outer_strides(o_io, n0, ts);
-                    BufRef       C;
-                    C.id          = BUF_TEMP;
-                    C.byte_off[0] = temp_alloc(total * csize_);
-                    {
-                        Step st;
-                        st.kind         = Step::EW;
-                        st.ew_kind      = B200FFT_EW_HERM2C_COPY;
-                        st.in           = in.buf;
-                        st.out          = C;
-                        st.ea.n         = (unsigned)n0;
-                        st.ea.iaux[0]   = (long long)n0;
-                        st.ea.in.es     = in.stride[0];
-                        st.ea.in.planar = in.buf.planar;
-                        st.ea.out.es    = 1;
-                        std::vector<OuterDim> o;
-                        for(size_t k = 0; k < o_io.size(); ++k)
-                            o.push_back({o_io[k].len, o_io[k].is, ts[k]});
-                        drop_unit_dims(o);
-                        fill_outer(o, st.ea, st.loops);
-                        st.in_elem_bytes  = elem_bytes(in.buf);
-                        st.out_elem_bytes = csize_;
-                        st.note           = "herm2c_copy";
-                        core_.steps.push_back(st);
-                    }
-                    Stage s;
-                    s.n  = n0;
-                    s.is = s.os = 1;
-                    s.outer.push_back({total / n0, (ptrdiff_t)n0, (ptrdiff_t)n0});
-                    s.in = s.out = C;
-                    s.inverse    = true;
-                    emit_c2c_1d(s);
-                    {
-                        Step st;
-                        st.kind         = Step::EW;
-                        st.ew_kind      = B200FFT_EW_C2R_COPY;
-                        st.in           = C;
-                        st.out          = out.buf;
-                        st.ea.n         = (unsigned)n0;
-                        st.ea.in.es     = 1;
-                        st.ea.out.es    = out.stride[0];
-                        st.ea.use_scale = use_scale;
-                        st.ea.scale     = scale;
-                        std::vector<OuterDim> o;
-                        for(size_t k = 0; k < o_io.size(); ++k)
-                            o.push_back({o_io[k].len, ts[k], o_io[k].os});
-                        drop_unit_dims(o);
-                        fill_outer(o, st.ea, st.loops);
-                        st.in_elem_bytes  = csize_;
-                        st.out_elem_bytes = rsize_;
-                        st.note           = "c2r_copy";
-                        core_.steps.push_back(st);
-                    }
-                }
-                temp_release(mark);
-            }
-
-            void plan_real_forward(const DataView& in, const DataView& out, double scale)
-            {
-                const size_t rank      = in.len.size();
-                const bool   use_scale = scale != 1.0;
-                plan_r2c_dim0(in, out, use_scale && rank == 1, scale);
-                for(size_t d = 1; d < rank; ++d)
-                {
-                    Stage s;
-                    s.n     = out.len[d];
-                    s.is    = out.stride[d];
-                    s.os    = out.stride[d];
-                    s.outer = outer_of(out, out, (int)d);
-                    s.in = s.out = out.buf;
-                    if(d == rank - 1 && use_scale)
-                    {
-                        s.use_scale = true;
-                        s.scale     = scale;
-                    }
-                    emit_c2c_1d(s);
-                }
-            }
-
-            void plan_real_inverse(const DataView& in, const DataView& out, double scale)
-            {
-                const size_t rank = out.len.size();
-                // higher dimensions first, in place on the Hermitian input (the
-                // interface allows a real-inverse transform to overwrite its input)
-                for(size_t d = rank; d-- > 1;)
-                {
-                    Stage s;
-                    s.n     = in.len[d];
-                    s.is    = in.stride[d];
-                    s.os    = in.stride[d];
-                    s.outer = outer_of(in, in, (int)d);
-                    s.in = s.out = in.buf;
-                    s.inverse    = true;
-                    emit_c2c_1d(s);
-                }
-                plan_c2r_dim0(in, out, scale != 1.0, scale);
-            }
-
-        private:
-            PlanCore& core_;
-            int       prec_;
-            size_t    rsize_, csize_;
-            size_t    temp_cur_ = 0;
-            std::map<std::pair<int, std::vector<int>>, const void*> tw_cache_;
-        };
-
         bool is_planar(rocfft_array_type t)
         {
             return t == rocfft_array_type_complex_planar || t == rocfft_array_type_hermitian_planar;

@@ -1,0 +1,62 @@
+"""Worker for the multi-GPU tests: one rank per GPU under torch.distributed.run.
+Runs a slab-decomposed 3D transform through the field/brick API and compares
+the gathered result with the CPU oracle on rank 0 (the reference's MPI worker,
+clients/tests/rocfft_mpi_worker.cpp, does the same against FFTW)."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    import torch
+    import rocfft_b200 as rf
+    from rocfft_b200 import distributed as D
+    from oracle import fft_oracle as orc
+
+    lengths = [int(v) for v in sys.argv[1].split("x")]
+    prec = sys.argv[2]
+    inverse = sys.argv[3] == "inv"
+    inplace = sys.argv[4] == "ip"
+    dist = D.init_process_group("nccl")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    assert rf.rocfft_setup() == 0
+    comm = D.create_nccl_comm(dist)
+    nx, ny, nz = lengths
+    lz = nz // world
+    cdt = np.complex64 if prec == "single" else np.complex128
+    full = orc.uniform_input((nz, ny, nx), cdt, seed=11)
+    mine = torch.from_numpy(full[rank * lz:(rank + 1) * lz].copy()).cuda()
+    out = mine if inplace else torch.empty_like(mine)
+    fft = D.SlabFFT3D(comm, rank, world, lengths,
+                      precision=rf.rocfft_precision_single if prec == "single" else rf.rocfft_precision_double,
+                      inverse=inverse, inplace=inplace, scale=0.5)
+    stream = torch.cuda.Stream()
+    fft.attach(torch, stream.cuda_stream)
+    for rep in range(2):  # twice: the second run exercises buffer reuse across calls
+        if rep == 1:
+            mine.copy_(torch.from_numpy(full[rank * lz:(rank + 1) * lz].copy()))
+            torch.cuda.synchronize()
+        st = fft.execute(mine.data_ptr(), None if inplace else out.data_ptr())
+        assert st == 0, st
+        torch.cuda.synchronize()
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    ok = True
+    if rank == 0:
+        got = torch.cat(gathered, dim=0).cpu().numpy()
+        ref = orc.c2c(full[None], +1 if inverse else -1)[0] * 0.5
+        ok, msg = orc.check_accuracy(got, ref, prec, nx * ny * nz)
+        print(f"mgpu {lengths} {prec} inverse={inverse} inplace={inplace} world={world}: {msg} -> {'ok' if ok else 'FAIL'}",
+              flush=True)
+    fft.destroy()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
