@@ -29,7 +29,9 @@
 namespace
 {
     // radices the pass engine may use; each gets a generated butterfly
-    const std::vector<int> kRadices = {2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16, 32};
+    const std::vector<int> kRadices = {2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16, 20, 25, 32};
+
+    bool is_bluestein_length(int n);
 
     // lengths with a single-kernel implementation; `small` selects a short
     // list for quick bring-up builds
@@ -39,6 +41,9 @@ namespace
         std::set<int> s;
         for(int n = 2; n <= 4096; n *= 2)
             s.insert(n);
+        for(int n = 32; n <= 20480; ++n)
+            if(is_bluestein_length(n) && (n <= 4096 || n % 1024 == 0))
+                s.insert(n);
         if(g_small)
         {
             for(int n : {3, 5, 6, 7, 9, 10, 11, 12, 13, 15, 20, 25, 27, 49, 50, 100, 125, 160, 200, 243, 500, 1000})
@@ -118,24 +123,68 @@ namespace
         return best;
     }
 
+    // Shapes measured to beat the heuristics on B200 (row kernels): length,
+    // precision (-1 = both) -> factor order, threads per transform, transforms
+    // per block, resident blocks.
+    struct Tuned
+    {
+        int              n, prec;
+        std::vector<int> f;
+        int              tpt, tpb, minb;
+    };
+    const std::vector<Tuned> kTuned = {
+        {500, 0, {20, 25}, 25, 8, 4},
+    };
+    const Tuned* tuned_for(int n, int prec)
+    {
+        for(const Tuned& t : kTuned)
+            if(t.n == n && (t.prec < 0 || t.prec == prec))
+                return &t;
+        return nullptr;
+    }
+
     struct Variant
     {
         const char* tag; // part of the kernel name
         int         id; // value stored in the pool (see launch.h)
         bool        col;
-        const char* iok;
+        const char* ioki;
+        const char* ioko;
         const char* cin;
         const char* cout_;
     };
     // ids must match enum b200fft_variant in launch/launch.h
     const Variant kVariants[] = {
-        {"row_unit", 0, false, "IO_UNIT", "COOP_NONE", "COOP_NONE"},
-        {"row_gen", 1, false, "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
-        {"col_str", 2, true, "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
-        {"col_gen", 3, true, "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
-        {"row_tout", 4, false, "IO_STRIDED", "COOP_NONE", "COOP_CFAST"},
-        {"col_rout", 5, true, "IO_STRIDED", "COOP_NONE", "COOP_EFAST"},
+        {"row_unit", 0, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        {"row_gen", 1, false, "IO_GENERIC", "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
+        {"col_str", 2, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
+        {"col_gen", 3, true, "IO_GENERIC", "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
+        {"row_tout", 4, false, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_CFAST"},
+        {"col_rout", 5, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_EFAST"},
+        {"col_blk", 6, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
+        {"row_r2c", 7, false, "IO_UNIT", "IO_GENERIC", "COOP_NONE", "COOP_R2C_POST"},
+        {"row_c2r", 8, false, "IO_GENERIC", "IO_UNIT", "COOP_C2R_PRE", "COOP_NONE"},
+        {"row_blue", 9, false, "IO_GENERIC", "IO_GENERIC", "COOP_NONE", "COOP_NONE"},
+        // persistent TMA-pipelined row kernels (stockham_rows_tma.cuh)
+        {"row_tma", 10, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        {"row_r2c_tma", 11, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        {"row_c2r_tma", 12, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
     };
+    const int kTmaStages = 3;
+    // padded lengths M with a single-kernel Bluestein: 2^k, 3*2^k, 5*2^k
+    bool is_bluestein_length(int n)
+    {
+        if(n < 32 || n > 20480)
+            return false;
+        for(int base : {1, 3, 5})
+            if(n % base == 0)
+            {
+                int r = n / base;
+                if((r & (r - 1)) == 0)
+                    return true;
+            }
+        return false;
+    }
 
     struct Kernel
     {
@@ -200,8 +249,20 @@ int main(int argc, char** argv)
             Choice ch = factorise(n, 16);
             if(!ch.ok)
                 continue;
+            // long lengths need more points per thread to stay within 1024 threads
+            if(n / *std::max_element(ch.f.begin(), ch.f.end()) > 1024)
+            {
+                if(prec == 1)
+                    continue;
+                ch = factorise(n, 32);
+                if(!ch.ok || n / *std::max_element(ch.f.begin(), ch.f.end()) > 1024)
+                    continue;
+            }
+            const Tuned* tuned = tuned_for(n, prec);
+            if(tuned)
+                ch.f = tuned->f;
             const int ept = *std::max_element(ch.f.begin(), ch.f.end());
-            const int tpt = n / ept;
+            const int tpt = tuned ? tuned->tpt : n / ept;
             for(const Variant& v : kVariants)
             {
                 // Launch shape.  Measured on B200: many small CTAs per SM overlap their
@@ -209,6 +270,16 @@ int main(int argc, char** argv)
                 // CTAs and column kernels at 64-byte-wide tiles, and the register cap
                 // is set so that as many CTAs as possible stay resident.
                 const bool coop    = strcmp(v.cin, "COOP_NONE") || strcmp(v.cout_, "COOP_NONE");
+                const bool realv   = v.id == 7 || v.id == 8; // fused even-length real kernels
+                if(realv && n < 4)
+                    continue;
+                if(v.id == 9 && !is_bluestein_length(n))
+                    continue;
+                if(n > 4096 && v.id != 0 && v.id != 1 && v.id != 9)
+                    continue; // long lengths: plain row kernels and Bluestein only
+                const bool tma = v.id >= 10 && v.id <= 12;
+                if(tma && (ch.f.size() < 2 || n < 16))
+                    continue;
                 const int  esz     = prec == 0 ? 8 : 16;
                 const int  npass   = (int)ch.f.size();
                 const int  regcap  = prec == 0 ? (v.col ? 64 : 80) : 128;
@@ -228,16 +299,38 @@ int main(int argc, char** argv)
                 else
                 {
                     tpb = std::max(1, std::min(64, 128 / tpt));
-                    if(coop)
+                    if(coop && !realv)
                         tpb = std::max(tpb, 128 / esz); // transposed stores need a wide tile
                     while(tpb > 1 && (tpt * tpb > max_thr || smem_bytes(n, tpb, false, prec, coop, npass) > smem_cap))
                         tpb /= 2;
                     if(tpt * tpb > 1024)
                         continue;
-                    if(coop && tpb * esz < 32)
+                    if(coop && !realv && tpb * esz < 32)
                         continue;
                 }
+                const bool tma_variant = v.id >= 10 && v.id <= 12;
+                if(tuned && !v.col && !(coop && !realv) && !tma_variant)
+                    tpb = tuned->tpb;
                 size_t sm = smem_bytes(n, tpb, v.col, prec, coop, npass);
+                if(tma)
+                {
+                    // rows travel as one contiguous byte range per tile: both the input and
+                    // the output tile must be a multiple of 16 bytes
+                    const int in_row  = v.id == 12 ? n + 1 : n;
+                    const int out_row = v.id == 11 ? n + 1 : n;
+                    auto aligned = [&](int w) { return (w * in_row * esz) % 16 == 0 && (w * out_row * esz) % 16 == 0; };
+                    int  w       = tpb;
+                    while(w > 1 && !aligned(w))
+                        --w;
+                    tpb = aligned(w) ? w : tpb * 2;
+                    if(tpt * tpb > max_thr)
+                        continue;
+                    const size_t stage = (((size_t)tpb * std::max(in_row, out_row) * esz + 15) / 16) * 16;
+                    const size_t work  = ((smem_bytes(n, tpb, false, prec, false, npass) + 15) / 16) * 16;
+                    sm                 = kTmaStages * stage + work + 8 * kTmaStages;
+                    if(2 * (sm + 1024) > 226 * 1024)
+                        continue; // fewer than two resident CTAs: the plain kernel does better
+                }
                 if(sm > smem_cap)
                     continue;
                 const int threads = tpt * tpb;
@@ -246,6 +339,8 @@ int main(int argc, char** argv)
                     minb = std::min<int>(minb, (int)(200 * 1024 / (sm + 1024)));
                 minb = std::max(1, std::min(minb, 2048 / threads));
                 minb = std::min(minb, 8);
+                if(tuned && !v.col && !(coop && !realv) && !tma_variant)
+                    minb = tuned->minb;
 
                 Kernel k;
                 k.n       = n;
@@ -264,7 +359,7 @@ int main(int argc, char** argv)
                 fl += ">";
                 k.cfg = std::string("KCfg<") + tname + "," + std::to_string(n) + ","
                         + std::to_string(tpt) + "," + std::to_string(tpb) + ","
-                        + (v.col ? "true" : "false") + "," + v.iok + "," + v.cin + "," + v.cout_ + ","
+                        + (v.col ? "true" : "false") + "," + v.ioki + "," + v.ioko + "," + v.cin + "," + v.cout_ + ","
                         + std::to_string(minb) + "," + fl + ">";
                 kernels.push_back(k);
             }
@@ -284,7 +379,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_engine.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -292,7 +387,14 @@ int main(int argc, char** argv)
         auto&         o = files[oi % nfiles];
         o << "extern \"C\" cudaError_t b200fft_launch_" << k.name
           << "(const b200fft_kargs* a, unsigned long long ntiles, cudaStream_t s)\n{\n"
-          << "    return launch_tile_kernel<" << k.cfg << ">(*a, ntiles, s);\n}\n\n";
+          << "    return ";
+        if(k.variant == 9)
+            o << "launch_bluestein_kernel<" << k.cfg << ">";
+        else if(k.variant >= 10 && k.variant <= 12)
+            o << "launch_rows_tma_kernel<" << k.cfg << ", " << (k.variant - 10) << ", " << kTmaStages << ">";
+        else
+            o << "launch_tile_kernel<" << k.cfg << ">";
+        o << "(*a, ntiles, s);\n}\n\n";
     }
 
     // ---- function pool ----

@@ -21,10 +21,10 @@ typedef struct b200fft_ioview
     long long es; // stride between consecutive points of one transform
     long long os[3]; // strides of the three outer (batch-like) dimensions
     int       planar; // 0 interleaved (or real), 1 planar
-    // Optional two-level stride along the transform (Stockham kernels with
-    // run-time strides only): point e lives at (e / blk) * bs + (e % blk) * es.
-    // Used to write (read) a transform dimension that is split into per-rank
-    // blocks of a packed exchange buffer.  blk == 0 switches it off.
+    // Two-level stride along the transform, honoured on the output side of the
+    // "blocked output" kernel variants only: point e lives at
+    // (e / blk) * bs + (e % blk) * es.  Used to write a transform dimension that
+    // is split into per-rank blocks of a packed exchange buffer.
     unsigned  blk;
     unsigned  blk_mul; // ceil(2^32 / blk), for an exact multiply-high division
     int       pad_;

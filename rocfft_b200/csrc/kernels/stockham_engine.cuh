@@ -64,12 +64,17 @@ namespace b200fft
         IO_UNIT    = 0, // interleaved complex, unit stride along the transform (both sides)
         IO_STRIDED = 1, // interleaved complex, run-time strides
         IO_GENERIC = 2, // interleaved or planar chosen at run time, run-time strides
+        IO_BLKOUT  = 3, // like IO_STRIDED, output with a two-level stride along the transform
     };
     enum CoopKind
     {
         COOP_NONE  = 0, // pass threads touch global memory themselves
         COOP_EFAST = 1, // staged through shared memory, consecutive threads walk a transform
         COOP_CFAST = 2, // staged, consecutive threads walk across the tile's transforms
+        // even-length real transforms fused into the half-length complex kernel
+        // (reference: library/src/rtc_realcomplex_gen.cpp:348-573, fused there only below length 512)
+        COOP_R2C_POST = 3, // output stage: Hermitian post-processing of the packed FFT
+        COOP_C2R_PRE  = 4, // input stage: Hermitian pre-processing into the packed FFT
     };
 
     // Kernel configuration; instantiated by generated code.
@@ -78,7 +83,8 @@ namespace b200fft
               int  TPT_,
               int  TPB_,
               bool COL_,
-              int  IOK_,
+              int  IOKI_,
+              int  IOKO_,
               int  CIN_,
               int  COUT_,
               int  MINB_,
@@ -92,7 +98,8 @@ namespace b200fft
         static constexpr int  TPT     = TPT_;
         static constexpr int  TPB     = TPB_;
         static constexpr bool COL     = COL_;
-        static constexpr int  IOK     = IOK_;
+        static constexpr int  IOKI    = IOKI_; // addressing of the input side
+        static constexpr int  IOKO    = IOKO_; // addressing of the output side
         static constexpr int  CIN     = CIN_;
         static constexpr int  COUT    = COUT_;
         static constexpr int  MINB    = MINB_;
@@ -120,16 +127,12 @@ namespace b200fft
     // ------------------------------------------------------------------
     // global-memory element access
     // ------------------------------------------------------------------
-    // offset of point e of a transform along its (possibly two-level) stride
+    // offset of point e of a transform along a two-level stride (v.blk >= 2)
     __device__ __forceinline__ long long elem_offset(const b200fft_ioview& v, int e)
     {
-        if(v.blk)
-        {
-            const unsigned q = __umulhi((unsigned)e, v.blk_mul);
-            const unsigned r = (unsigned)e - q * v.blk;
-            return (long long)q * v.bs + (long long)r * v.es;
-        }
-        return (long long)e * v.es;
+        const unsigned q = __umulhi((unsigned)e, v.blk_mul);
+        const unsigned r = (unsigned)e - q * v.blk;
+        return (long long)q * v.bs + (long long)r * v.es;
     }
 
     template <class C>
@@ -139,17 +142,17 @@ namespace b200fft
         using T  = typename C::T;
         using T2 = typename C::T2;
         T2 r;
-        if constexpr(C::IOK == IO_UNIT)
+        if constexpr(C::IOKI == IO_UNIT)
         {
             r = reinterpret_cast<const T2*>(v.p[0])[base + e];
         }
-        else if constexpr(C::IOK == IO_STRIDED)
+        else if constexpr(C::IOKI == IO_STRIDED || C::IOKI == IO_BLKOUT)
         {
-            r = reinterpret_cast<const T2*>(v.p[0])[base + elem_offset(v, e)];
+            r = reinterpret_cast<const T2*>(v.p[0])[base + (long long)e * v.es];
         }
         else
         {
-            const long long off = base + elem_offset(v, e);
+            const long long off = base + (long long)e * v.es;
             if(v.planar)
             {
                 r.x = reinterpret_cast<const T*>(v.p[0])[off];
@@ -179,17 +182,21 @@ namespace b200fft
             val.x *= scale;
             val.y *= scale;
         }
-        if constexpr(C::IOK == IO_UNIT)
+        if constexpr(C::IOKO == IO_UNIT)
         {
             reinterpret_cast<T2*>(v.p[0])[base + e] = val;
         }
-        else if constexpr(C::IOK == IO_STRIDED)
+        else if constexpr(C::IOKO == IO_STRIDED)
+        {
+            reinterpret_cast<T2*>(v.p[0])[base + (long long)e * v.es] = val;
+        }
+        else if constexpr(C::IOKO == IO_BLKOUT)
         {
             reinterpret_cast<T2*>(v.p[0])[base + elem_offset(v, e)] = val;
         }
         else
         {
-            const long long off = base + elem_offset(v, e);
+            const long long off = base + (long long)e * v.es;
             if(v.planar)
             {
                 reinterpret_cast<T*>(v.p[0])[off] = val.x;
@@ -361,27 +368,99 @@ namespace b200fft
         const long long obase = view_base(a.out, tp.i0_first + c, tp.i1, tp.i2);
 
         // ---- cooperative load stage ----
-        if constexpr(C::CIN != COOP_NONE)
+        if constexpr(C::CIN == COOP_C2R_PRE)
         {
-            for(int idx = tid; idx < C::N * C::TPB; idx += C::THREADS)
+            // in: Hermitian rows X[0..h] (h = N); shared memory receives Z' with
+            // Z'_p = (X_p + conj X_q) + i conj(W^p) (X_p - conj X_q),  q = h - p,
+            // whose unnormalised inverse FFT is the packed real row.  Stored with
+            // parts exchanged: the forward passes then compute the inverse.
+            constexpr int H     = C::N;
+            constexpr int NP    = H / 2 + 1;
+            constexpr int ITEMS = NP * C::TPB;
+            constexpr int ITER  = (ITEMS + C::THREADS - 1) / C::THREADS;
+            constexpr int UNR   = ITER < 8 ? ITER : 8; // loads in flight per thread
+            const T2* __restrict__ htw = reinterpret_cast<const T2*>(a.aux[0]);
+            for(int it0 = 0; it0 < ITER; it0 += UNR)
             {
-                int cc, e;
-                if constexpr(C::CIN == COOP_EFAST)
+                T2 xa[UNR], xb[UNR], w[UNR];
+#pragma unroll
+                for(int u = 0; u < UNR; ++u)
                 {
-                    cc = idx / C::N;
-                    e  = idx % C::N;
+                    const int idx = tid + (it0 + u) * C::THREADS;
+                    const int cc  = idx / NP;
+                    const int p   = idx % NP;
+                    xa[u].x = xa[u].y = xb[u].x = xb[u].y = 0;
+                    w[u].x = w[u].y = 0;
+                    if(idx < ITEMS && (unsigned)cc < nvalid)
+                    {
+                        xa[u] = gload<C>(a.in, bases[2 * cc], p, false);
+                        xb[u] = gload<C>(a.in, bases[2 * cc], H - p, false);
+                        w[u]  = htw[p];
+                    }
                 }
-                else
+#pragma unroll
+                for(int u = 0; u < UNR; ++u)
                 {
-                    cc = idx % C::TPB;
-                    e  = idx / C::TPB;
+                    const int idx = tid + (it0 + u) * C::THREADS;
+                    if(idx >= ITEMS)
+                        continue;
+                    const int cc = idx / NP;
+                    const int p  = idx % NP;
+                    const int q  = H - p;
+                    T2        a0 = xa[u], b0 = xb[u];
+                    if(p == 0)
+                    {
+                        a0.y = 0; // imaginary parts of DC and Nyquist carry no information
+                        b0.y = 0;
+                    }
+                    b0.y = -b0.y;
+                    T2 e, d, t;
+                    e.x = a0.x + b0.x;
+                    e.y = a0.y + b0.y;
+                    d.x = a0.x - b0.x;
+                    d.y = a0.y - b0.y;
+                    t.x = w[u].y; // i * conj(W^p)
+                    t.y = w[u].x;
+                    const T2 td = cmul(t, d);
+                    T2       zp, zq;
+                    zp.x = e.x + td.x;
+                    zp.y = e.y + td.y;
+                    zq.x = e.x - td.x;
+                    zq.y = -(e.y - td.y);
+                    sm[C::sidx(cc, p)] = cswap(zp);
+                    if(p != q && p != 0)
+                        sm[C::sidx(cc, q)] = cswap(zq);
                 }
-                T2 v;
-                v.x = 0;
-                v.y = 0;
-                if((unsigned)cc < nvalid)
-                    v = gload<C>(a.in, bases[2 * cc], e, inverse);
-                sm[C::sidx(cc, e)] = v;
+            }
+            __syncthreads();
+        }
+        else if constexpr(C::CIN != COOP_NONE)
+        {
+            constexpr int ITEMS = C::N * C::TPB;
+            constexpr int ITER  = (ITEMS + C::THREADS - 1) / C::THREADS;
+            constexpr int UNR   = ITER < 8 ? ITER : 8; // loads in flight per thread
+            for(int it0 = 0; it0 < ITER; it0 += UNR)
+            {
+                T2 v[UNR];
+#pragma unroll
+                for(int u = 0; u < UNR; ++u)
+                {
+                    const int idx = tid + (it0 + u) * C::THREADS;
+                    const int cc  = (C::CIN == COOP_EFAST) ? idx / C::N : idx % C::TPB;
+                    const int e   = (C::CIN == COOP_EFAST) ? idx % C::N : idx / C::TPB;
+                    v[u].x = v[u].y = 0;
+                    if(idx < ITEMS && (unsigned)cc < nvalid)
+                        v[u] = gload<C>(a.in, bases[2 * cc], e, inverse);
+                }
+#pragma unroll
+                for(int u = 0; u < UNR; ++u)
+                {
+                    const int idx = tid + (it0 + u) * C::THREADS;
+                    const int cc  = (C::CIN == COOP_EFAST) ? idx / C::N : idx % C::TPB;
+                    const int e   = (C::CIN == COOP_EFAST) ? idx % C::N : idx / C::TPB;
+                    if(idx < ITEMS)
+                        sm[C::sidx(cc, e)] = v[u];
+                }
             }
             __syncthreads();
         }
@@ -413,7 +492,64 @@ namespace b200fft
             run_passes<C, 0, false, false>(t, c, sm, tw, g_src, g_dst);
 
         // ---- cooperative store stage ----
-        if constexpr(C::COUT != COOP_NONE)
+        if constexpr(C::COUT == COOP_R2C_POST)
+        {
+            // shared memory holds Z = FFT_h of the packed real row (h = N); write
+            // X_p = e + t d,  X_q = conj(e - t d),  e = (Z_p + conj Z_q)/2,
+            // d = (Z_p - conj Z_q)/2,  t = -i W^p,  q = h - p.
+            constexpr int H     = C::N;
+            constexpr int NP    = H / 2 + 1;
+            constexpr int ITEMS = NP * C::TPB;
+            constexpr int ITER  = (ITEMS + C::THREADS - 1) / C::THREADS;
+            const T2* __restrict__ htw = reinterpret_cast<const T2*>(a.aux[0]);
+            const T sc = use_sc ? scale : (T)1;
+#pragma unroll 4
+            for(int it = 0; it < ITER; ++it)
+            {
+                const int idx = tid + it * C::THREADS;
+                if(idx >= ITEMS)
+                    break;
+                const int cc = idx / NP;
+                const int p  = idx % NP;
+                const int q  = H - p;
+                if((unsigned)cc >= nvalid)
+                    continue;
+                const long long ob = bases[2 * cc + 1];
+                if(p == 0)
+                {
+                    const T2 z = sm[C::sidx(cc, 0)];
+                    T2       x0, xh;
+                    x0.x = (z.x + z.y) * sc;
+                    x0.y = 0;
+                    xh.x = (z.x - z.y) * sc;
+                    xh.y = 0;
+                    gstore<C>(a.out, ob, 0, x0, false, false, (T)1);
+                    gstore<C>(a.out, ob, H, xh, false, false, (T)1);
+                    continue;
+                }
+                const T2 za = sm[C::sidx(cc, p)];
+                T2       zb = sm[C::sidx(cc, q)];
+                zb.y        = -zb.y;
+                const T2 w  = htw[p];
+                T2       e, d, t;
+                e.x = (za.x + zb.x) * (T)0.5;
+                e.y = (za.y + zb.y) * (T)0.5;
+                d.x = (za.x - zb.x) * (T)0.5;
+                d.y = (za.y - zb.y) * (T)0.5;
+                t.x = w.y; // -i * W^p
+                t.y = -w.x;
+                const T2 td = cmul(t, d);
+                T2       xp, xq;
+                xp.x = (e.x + td.x) * sc;
+                xp.y = (e.y + td.y) * sc;
+                xq.x = (e.x - td.x) * sc;
+                xq.y = -(e.y - td.y) * sc;
+                gstore<C>(a.out, ob, p, xp, false, false, (T)1);
+                if(p != q)
+                    gstore<C>(a.out, ob, q, xq, false, false, (T)1);
+            }
+        }
+        else if constexpr(C::COUT != COOP_NONE)
         {
             // run_passes ended with a barrier because the last pass wrote shared memory
             for(int idx = tid; idx < C::N * C::TPB; idx += C::THREADS)
@@ -433,6 +569,89 @@ namespace b200fft
                     gstore<C>(a.out, bases[2 * cc + 1], e, sm[C::sidx(cc, e)], inverse, use_sc, scale);
             }
         }
+    }
+
+    // ------------------------------------------------------------------
+    // Bluestein's algorithm for one tile, entirely in shared memory
+    // ------------------------------------------------------------------
+    // Transforms of arbitrary length n <= (M + 1) / 2 with M = C::N:
+    //   a = x * chirp, zero padded to M;  A = FFT_M(a);  A *= filter;
+    //   y = IFFT_M(A);  X_k = y_k * chirp_k          (chirp_p = exp(-i pi p^2 / n),
+    //   filter = FFT_M(wrapped conj chirp) / M, both tables made on the host).
+    // The chirp multiply rides on the first pass's global loads, the filter
+    // multiply on the first pass of the second FFT and the final chirp
+    // multiply on the last pass's global stores, so the kernel makes a single
+    // HBM round trip over n points per transform.  The reference reaches this
+    // form only up to M = 4096 (library/src/tree_node_bluestein.cpp:416-420);
+    // 227 KB of shared memory per CTA carry it to M = 20480 in single precision.
+    // kargs: iaux[0] = n, aux[0] = chirp (n entries), aux[1] = filter (M entries).
+    template <class C>
+    __global__ void __launch_bounds__(C::THREADS, C::MINB)
+        bluestein_tile_kernel(const __grid_constant__ b200fft_kargs a)
+    {
+        using T  = typename C::T;
+        using T2 = typename C::T2;
+        extern __shared__ __align__(16) unsigned char smem_raw[];
+        T2* sm = reinterpret_cast<T2*>(smem_raw);
+
+        const int     tid     = threadIdx.x;
+        const int     c       = tid / C::TPT;
+        const int     t       = tid % C::TPT;
+        const TilePos tp      = decode_tile(a, blockIdx.x, C::TPB);
+        const bool    inverse = a.inverse != 0;
+        const bool    use_sc  = a.use_scale != 0;
+        const T       scale   = (T)a.scale;
+        const int     n       = (int)a.iaux[0];
+        const T2* __restrict__ tw    = reinterpret_cast<const T2*>(a.twiddles);
+        const T2* __restrict__ chirp = reinterpret_cast<const T2*>(a.aux[0]);
+        const T2* __restrict__ filt  = reinterpret_cast<const T2*>(a.aux[1]);
+
+        const unsigned  nvalid = min((unsigned)C::TPB, a.on[0] - tp.i0_first);
+        const bool      valid  = (unsigned)c < nvalid;
+        const long long ibase  = view_base(a.in, tp.i0_first + c, tp.i1, tp.i2);
+        const long long obase  = view_base(a.out, tp.i0_first + c, tp.i1, tp.i2);
+
+        auto src1 = [&](int e) -> T2 {
+            T2 v;
+            v.x = 0;
+            v.y = 0;
+            if(valid && e < n)
+                v = cmul(gload<C>(a.in, ibase, e, inverse), chirp[e]);
+            return v;
+        };
+        auto s_dst = [=](int e, T2 v) { sm[C::sidx(c, e)] = v; };
+        run_passes<C, 0, false, true>(t, c, sm, tw, src1, s_dst);
+
+        // second transform: inverse FFT as a forward FFT on exchanged parts
+        auto src2 = [=](int e) -> T2 { return cswap(cmul(sm[C::sidx(c, e)], filt[e])); };
+        auto dst2 = [&](int e, T2 v) {
+            if(valid && e < n)
+                gstore<C>(a.out, obase, e, cmul(cswap(v), chirp[e]), inverse, use_sc, scale);
+        };
+        run_passes<C, 0, true, false>(t, c, sm, tw, src2, dst2);
+    }
+
+    template <class C>
+    cudaError_t launch_bluestein_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
+    {
+        static bool attr_done[64] = {};
+        int         dev           = 0;
+        cudaGetDevice(&dev);
+        if(C::SMEM_BYTES > 48 * 1024 && dev < 64 && !attr_done[dev])
+        {
+            cudaError_t e = cudaFuncSetAttribute(bluestein_tile_kernel<C>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)C::SMEM_BYTES);
+            if(e != cudaSuccess)
+                return e;
+            attr_done[dev] = true;
+        }
+        if(ntiles == 0)
+            return cudaSuccess;
+        if(ntiles > 0x7fffffffull)
+            return cudaErrorInvalidConfiguration;
+        bluestein_tile_kernel<C><<<(unsigned)ntiles, C::THREADS, C::SMEM_BYTES, stream>>>(a);
+        return cudaGetLastError();
     }
 
     // host-side launch helper used by generated launchers

@@ -26,6 +26,15 @@ typedef enum b200fft_variant
     B200FFT_COL_GEN  = 3, // columns, any stride / planar
     B200FFT_ROW_TOUT = 4, // rows in, columns out (transposing store) (CS_KERNEL_STOCKHAM_BLOCK_RC)
     B200FFT_COL_ROUT = 5, // columns in, rows out                     (CS_KERNEL_STOCKHAM_BLOCK_CR)
+    B200FFT_COL_BLK  = 6, // columns, output split into per-rank blocks (multi-device exchange buffers)
+    B200FFT_ROW_R2C  = 7, // rows of packed reals in, Hermitian rows out (length = half the real length)
+    B200FFT_ROW_C2R  = 8, // Hermitian rows in, rows of packed reals out
+    B200FFT_ROW_BLUE = 9, // whole Bluestein transform in one kernel; `length` is the padded length M
+    // persistent kernels that move contiguous row tiles with the bulk-copy engine (TMA);
+    // they need 16-byte aligned base pointers and back-to-back rows
+    B200FFT_ROW_TMA     = 10,
+    B200FFT_ROW_R2C_TMA = 11,
+    B200FFT_ROW_C2R_TMA = 12,
 } b200fft_variant;
 
 typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);

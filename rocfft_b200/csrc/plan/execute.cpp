@@ -6,6 +6,7 @@
 // Nothing here synchronises: all work is asynchronous on the caller's stream.
 #include "plan.h"
 #include <atomic>
+#include <cstdint>
 
 namespace b200fft
 {
@@ -101,7 +102,15 @@ namespace b200fft
                     a.in.p[1]       = ipp[1];
                     a.out.p[0]      = opp[0];
                     a.out.p[1]      = opp[1];
-                    e = s.kern->launch(&a, s.ntiles, stream);
+                    const bool misaligned
+                        = ((reinterpret_cast<uintptr_t>(ipp[0]) | reinterpret_cast<uintptr_t>(opp[0])) & 15u) != 0;
+                    if(s.kern_unaligned && misaligned)
+                    {
+                        a.ntile0 = s.ntile0_unaligned;
+                        e        = s.kern_unaligned->launch(&a, s.ntiles_unaligned, stream);
+                    }
+                    else
+                        e = s.kern->launch(&a, s.ntiles, stream);
                 }
                 if(e != cudaSuccess)
                     return rocfft_status_failure;

@@ -102,6 +102,10 @@ namespace b200fft
         } kind
             = TILE;
         const b200fft_pool_entry* kern    = nullptr;
+        // when set, `kern` needs 16-byte aligned base pointers and this one is used otherwise
+        const b200fft_pool_entry* kern_unaligned = nullptr;
+        unsigned                  ntile0_unaligned = 0;
+        unsigned long long        ntiles_unaligned = 0;
         int                       ew_kind = 0;
         int                       fused_id = 0;
         b200fft_kargs             ka{};
@@ -128,6 +132,7 @@ namespace b200fft
         std::vector<void*> tables; // cudaMalloc'd, freed with the plan
         int               device = 0;
         bool              host_only = false; // built without a GPU: inspectable, not executable
+        int*              dev_error = nullptr; // raised by kernels whose bounded waits expire
         ~PlanCore();
     };
 }

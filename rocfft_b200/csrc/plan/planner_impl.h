@@ -5,6 +5,7 @@
 #include "plan.h"
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <sstream>
@@ -29,9 +30,15 @@ namespace b200fft
             bool                  inverse   = false;
             bool                  use_scale = false;
             double                scale     = 1.0;
-            // optional two-level stride along the transform (see b200fft_ioview::blk)
-            size_t    in_blk = 0, out_blk = 0;
-            ptrdiff_t in_bs = 0, out_bs = 0;
+            // optional two-level output stride along the transform (see b200fft_ioview::blk)
+            size_t    out_blk = 0;
+            ptrdiff_t out_bs  = 0;
+            // fused kernels: a specific pool variant and its extra table
+            int         force_variant = -1;
+            const void* aux0          = nullptr;
+            const void* aux1          = nullptr;
+            long long   iaux0         = 0;
+            size_t      kernel_length = 0; // pool length when it differs from n (Bluestein: padded length)
         };
 
         inline const b200fft_pool_entry* pool_find(size_t n, int prec, int variant)
@@ -118,6 +125,15 @@ namespace b200fft
                 if(cudaMemcpy(d, host.data(), host.size(), cudaMemcpyHostToDevice) != cudaSuccess)
                     throw std::runtime_error("device table upload failed");
                 return d;
+            }
+            const void* device_error_flag()
+            {
+                if(!core_.dev_error && !core_.host_only)
+                {
+                    std::vector<char> z(16, 0);
+                    core_.dev_error = static_cast<int*>(const_cast<void*>(upload(z)));
+                }
+                return core_.dev_error;
             }
             const void* stacked_twiddles(const b200fft_pool_entry* k)
             {
@@ -310,7 +326,7 @@ namespace b200fft
                     emit_tile(s);
                     return;
                 }
-                if(s.in_blk || s.out_blk)
+                if(s.out_blk)
                     throw std::runtime_error("blocked strides need a single-kernel length");
                 size_t n1, n2;
                 bool   smooth = true;
@@ -353,10 +369,24 @@ namespace b200fft
 
                 const b200fft_pool_entry* kern    = nullptr;
                 int                       tiledim = -1;
-                const bool blocked = s.in_blk || s.out_blk;
-                if(s.is == 1 && s.os == 1)
+                const bool blocked = s.out_blk >= 2;
+                if(s.force_variant >= 0)
                 {
-                    kern = pool_find(s.n, prec_, (il && !blocked) ? B200FFT_ROW_UNIT : B200FFT_ROW_GEN);
+                    kern = pool_find(s.kernel_length ? s.kernel_length : s.n, prec_, s.force_variant);
+                    if(!kern)
+                        throw std::runtime_error("fused kernel variant missing");
+                }
+                else if(blocked)
+                {
+                    int k = find_dim(true, true);
+                    kern  = il ? pool_find(s.n, prec_, B200FFT_COL_BLK) : nullptr;
+                    if(k < 0 || !kern)
+                        throw std::runtime_error("blocked output needs an interleaved column tile");
+                    tiledim = k;
+                }
+                else if(s.is == 1 && s.os == 1)
+                {
+                    kern = pool_find(s.n, prec_, il ? B200FFT_ROW_UNIT : B200FFT_ROW_GEN);
                 }
                 else
                 {
@@ -415,14 +445,47 @@ namespace b200fft
                     else if(blk == 1)
                         v.es = bs; // blocks of one point: a plain stride
                 };
-                set_blk(a.in, s.in_blk, s.in_bs);
                 set_blk(a.out, s.out_blk, s.out_bs);
                 fill_outer(o, a, st.loops);
+                // contiguous rows: prefer the persistent TMA-pipelined kernel
+                {
+                    int tma_variant = -1;
+                    size_t in_row = s.n, out_row = s.n;
+                    if(kern->variant == B200FFT_ROW_UNIT)
+                        tma_variant = B200FFT_ROW_TMA;
+                    else if(kern->variant == B200FFT_ROW_R2C && !s.out.planar && s.os == 1)
+                    {
+                        tma_variant = B200FFT_ROW_R2C_TMA;
+                        out_row     = s.n + 1;
+                    }
+                    else if(kern->variant == B200FFT_ROW_C2R && !s.in.planar && s.is == 1)
+                    {
+                        tma_variant = B200FFT_ROW_C2R_TMA;
+                        in_row      = s.n + 1;
+                    }
+                    const b200fft_pool_entry* tk
+                        = tma_variant >= 0 ? pool_find(s.kernel_length ? s.kernel_length : s.n, prec_, tma_variant) : nullptr;
+                    const bool rows_back_to_back = o.size() <= 1 && st.loops.empty()
+                                                   && (o.empty() || ((size_t)o[0].is == in_row && (size_t)o[0].os == out_row));
+                    const bool offsets_ok = (s.in.byte_off[0] % 16 == 0) && (s.out.byte_off[0] % 16 == 0);
+                    if(tk && rows_back_to_back && offsets_ok && !getenv("ROCFFT_B200_NO_TMA"))
+                    {
+                        st.kern_unaligned   = kern;
+                        st.ntile0_unaligned = (a.on[0] + kern->tpb - 1) / kern->tpb;
+                        st.ntiles_unaligned = (unsigned long long)st.ntile0_unaligned * a.on[1] * a.on[2];
+                        kern                = tk;
+                        st.kern             = tk;
+                        a.aux[3]            = device_error_flag();
+                    }
+                }
                 a.ntile0    = (a.on[0] + kern->tpb - 1) / kern->tpb;
                 a.inverse   = s.inverse;
                 a.use_scale = s.use_scale;
                 a.scale     = s.scale;
                 a.twiddles  = stacked_twiddles(kern);
+                a.aux[0]    = s.aux0 ? s.aux0 : a.aux[0];
+                a.aux[1]    = s.aux1;
+                a.iaux[0]   = s.iaux0;
                 st.ntiles   = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];
                 st.in_elem_bytes  = elem_bytes(s.in);
                 st.out_elem_bytes = elem_bytes(s.out);
@@ -511,8 +574,35 @@ namespace b200fft
                 temp_release(mark);
             }
 
+            // smallest padded length >= 2n-1 that has a single-kernel Bluestein, or 0
+            size_t fused_bluestein_length(size_t n) const
+            {
+                size_t                    cnt = 0, best = 0;
+                const b200fft_pool_entry* p   = b200fft_pool(&cnt);
+                for(size_t i = 0; i < cnt; ++i)
+                    if(p[i].variant == B200FFT_ROW_BLUE && p[i].precision == prec_
+                       && (size_t)p[i].length >= 2 * n - 1 && (!best || (size_t)p[i].length < best))
+                        best = p[i].length;
+                return best;
+            }
+
             void emit_bluestein(const Stage& s)
             {
+                if(const size_t mf = fused_bluestein_length(s.n))
+                {
+                    std::vector<char> h;
+                    host_chirp(s.n, prec_, h);
+                    const void* chirp = upload(h);
+                    host_bluestein_filter(s.n, mf, prec_, h);
+                    Stage f         = s;
+                    f.force_variant = B200FFT_ROW_BLUE;
+                    f.kernel_length = mf;
+                    f.aux0          = chirp;
+                    f.aux1          = upload(h);
+                    f.iaux0         = (long long)s.n;
+                    emit_tile(f);
+                    return;
+                }
                 const size_t           m    = choose_bluestein_length(s.n);
                 const size_t           mark = temp_mark();
                 std::vector<ptrdiff_t> ts;
@@ -679,7 +769,29 @@ namespace b200fft
                 std::vector<OuterDim> o_in = outer_of(in, out, 0); // (len, real strides, herm strides)
                 // lengths of outer dims are the same on both sides
                 std::vector<ptrdiff_t> ts;
-                if(even_ok)
+                if(even_ok && pool_find(n0 / 2, prec_, B200FFT_ROW_R2C))
+                {
+                    // one kernel: packed half-length FFT with the Hermitian post-processing
+                    // done on the tile while it is still in shared memory
+                    std::vector<char> hbuf;
+                    host_half_twiddles(n0, prec_, hbuf);
+                    Stage s;
+                    s.n  = n0 / 2;
+                    s.is = 1;
+                    s.os = out.stride[0];
+                    for(size_t k = 0; k < o_in.size(); ++k)
+                        s.outer.push_back({o_in[k].len, o_in[k].is / 2, o_in[k].os});
+                    s.in            = in.buf; // real pairs read as complex
+                    s.in.planar     = false;
+                    s.out           = out.buf;
+                    s.use_scale     = use_scale;
+                    s.scale         = scale;
+                    s.force_variant = B200FFT_ROW_R2C;
+                    s.aux0          = upload(hbuf);
+                    drop_unit_dims(s.outer);
+                    emit_tile(s);
+                }
+                else if(even_ok)
                 {
                     const size_t h     = n0 / 2;
                     const size_t total = temp_outer_strides(o_in, h, ts);
@@ -782,7 +894,28 @@ namespace b200fft
                     o_io.push_back({out.len[k], in.stride[k], out.stride[k]});
                 o_io.push_back({in.batch, in.dist, out.dist});
                 std::vector<ptrdiff_t> ts;
-                if(even_ok)
+                if(even_ok && pool_find(n0 / 2, prec_, B200FFT_ROW_C2R))
+                {
+                    std::vector<char> hbuf;
+                    host_half_twiddles(n0, prec_, hbuf);
+                    Stage s;
+                    s.n  = n0 / 2;
+                    s.is = in.stride[0];
+                    s.os = 1;
+                    for(size_t k = 0; k < o_io.size(); ++k)
+                        s.outer.push_back({o_io[k].len, o_io[k].is, o_io[k].os / 2});
+                    s.in            = in.buf;
+                    s.out           = out.buf; // real pairs written as complex
+                    s.out.planar    = false;
+                    s.inverse       = true;
+                    s.use_scale     = use_scale;
+                    s.scale         = scale;
+                    s.force_variant = B200FFT_ROW_C2R;
+                    s.aux0          = upload(hbuf);
+                    drop_unit_dims(s.outer);
+                    emit_tile(s);
+                }
+                else if(even_ok)
                 {
                     const size_t h     = n0 / 2;
                     const size_t total = temp_outer_strides(o_io, h, ts);

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 POW2 = [2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096]
 MIXED = [3, 5, 6, 7, 9, 10, 11, 12, 13, 15, 20, 25, 27, 49, 50, 100, 125, 160, 200, 243, 500, 1000]
-PRIMES_ETC = [17, 19, 23, 31, 37, 97, 127, 211, 509, 1021, 4099]  # Bluestein
+PRIMES_ETC = [17, 19, 23, 31, 37, 97, 127, 211, 509, 1021, 4099, 10007, 10243, 20011]  # Bluestein
 LARGE = [8192, 16384, 65536, 20480, 40000, 1 << 20]  # two-kernel decompositions
 UNPOOLED = [14, 18, 21, 22, 24, 26, 28, 30, 36, 77, 120, 143, 1001, 3000, 6000]
 
@@ -68,7 +68,7 @@ def cases_layout():
         # in-place with differing layouts goes through scratch
         out.append(Case(C2C_FWD, prec, [16], 4, IP, CI, CI, [1], [2], 16, 40))
         # without a caller-supplied work buffer the library allocates its own
-        out.append(Case(C2C_FWD, prec, [8192], 2, IP, user_work_buffer=False))
+        out.append(Case(C2C_FWD, prec, [1 << 17], 2, IP, user_work_buffer=False))
         out.append(Case(C2C_FWD, prec, [1], 5, OOP))
     return out
 
@@ -168,9 +168,9 @@ def test_work_buffer_contract(gpu):
     (reference: clients/tests/unit_test.cpp:256-345)."""
     import torch
     import rocfft_b200 as rf
-    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [8192], 2)
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1 << 17], 2)
     assert p.work_bytes > 0
-    x = torch.zeros(2 * 8192, dtype=torch.complex64, device="cuda")
+    x = torch.zeros(2 << 17, dtype=torch.complex64, device="cuda")
     small = torch.empty(16, dtype=torch.uint8, device="cuda")
     assert p.set_work_buffer(small.data_ptr(), 16) == rf.rocfft_status_success
     assert p.execute([x.data_ptr()]) == rf.rocfft_status_invalid_work_buffer

@@ -139,10 +139,19 @@ def test_planner_choices_for_benchmark_configs(L):
     # config 5: three in-place passes
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
     assert "steps: 3" in describe(L, p) and p.work_bytes == 0
-    # config 4: prime length goes through Bluestein
+    # config 4: prime length goes through the single-kernel Bluestein with M = 20480
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)
-    assert "bluestein" in describe(L, p)
-    assert p.work_bytes > 0
+    text = describe(L, p)
+    assert "steps: 1" in text and "len20480_row_blue" in text and p.work_bytes == 0
+    # a prime too long for one CTA's shared memory takes the multi-kernel Bluestein path
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [100003], 4)
+    assert "bluestein_pad_mul" in describe(L, p) and p.work_bytes > 0
+    # config 2: even-length real transforms are one fused kernel each way
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_real_forward, 0, [1000], 65536)
+    text = describe(L, p)
+    assert "steps: 1" in text and "len500_row_r2c" in text and p.work_bytes == 0
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_real_inverse, 0, [1000], 65536)
+    assert "len500_row_c2r" in describe(L, p)
 
 
 def test_stacked_twiddle_table_matches_pass_model(L):
