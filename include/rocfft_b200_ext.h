@@ -40,6 +40,26 @@ ROCFFT_EXPORT rocfft_status b200fft_nccl_unique_id(void* id128);
 ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_create(int nranks, int rank, const void* id128, void** comm);
 ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_destroy(void* comm);
 
+/* Batched 1D complex transform that allocates no device memory, for callers
+ * that may not call cudaMalloc where they run the transform (a real-time
+ * loop that must not take the allocator's locks, a process whose device
+ * memory was handed out once and frozen, ...).  It has no counterpart in the
+ * reference: rocFFT always allocates twiddle tables at plan creation and may
+ * allocate a work buffer at execute time.
+ *
+ * Single precision, interleaved, unit stride, `batch` rows of `length` points
+ * back to back; in == out is allowed.  `length` must be a power of two from 256
+ * to 1048576 and length * batch * 8 bytes must not exceed 4 MiB
+ * (rocfft_status_invalid_arg_value otherwise): the intermediate array lives in a
+ * 4 MiB + 64 KiB __device__ array inside the library image, which every GPU
+ * that loads the library holds until the process exits.  `stream` is a
+ * cudaStream_t.  The first call on a device, and the first call after `length`
+ * changes, copies small tables synchronously — make that call before any
+ * stream capture begins.  All calls share the array: calls that overlap on the
+ * GPU race, so serialise them. */
+ROCFFT_EXPORT rocfft_status b200fft_c2c_1d_static_scratch(
+    const void* in, void* out, size_t length, size_t batch, int inverse, void* stream);
+
 /* Number of GPU kernels this library has launched in the calling process. */
 ROCFFT_EXPORT unsigned long long b200fft_launch_count();
 

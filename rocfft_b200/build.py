@@ -34,7 +34,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", INCLUDE,
              "-I", os.path.join(CSRC, "launch"), "-I", os.path.join(CSRC, "kernels"), "-Wall"]
 
 HOST_SOURCES = ["api/api.cpp", "plan/planner.cpp", "plan/twiddles.cpp", "plan/execute.cpp", "mgpu/mgpu.cpp"]
-CUDA_SOURCES = ["launch/elementwise.cu"]
+CUDA_SOURCES = ["launch/elementwise.cu", "launch/noalloc.cu"]
 
 
 def _digest(paths, extra=""):
@@ -55,6 +55,7 @@ def _deps_text():
             if f.endswith((".h", ".cuh")):
                 hs.append(os.path.join(root, f))
     hs.append(os.path.join(INCLUDE, "rocfft", "rocfft.h"))
+    hs.append(os.path.join(INCLUDE, "rocfft_b200_ext.h"))
     return sorted(hs)
 
 
