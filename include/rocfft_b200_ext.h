@@ -60,6 +60,22 @@ ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_destroy(void* comm);
 ROCFFT_EXPORT rocfft_status b200fft_c2c_1d_static_scratch(
     const void* in, void* out, size_t length, size_t batch, int inverse, void* stream);
 
+/* The exchange schedule of a slab-decomposed 3D plan, as pure host arithmetic:
+ * byte offsets (relative to the send buffer and to the receive buffer) and the
+ * size of the block exchanged with each of `ranks` peers in chunk `chunk` of the
+ * first (`first` != 0) or second global transpose.  This is the function the
+ * executor itself calls (reference counterpart: the offsets built in
+ * GlobalTransposeA2A, library/src/plan.cpp:2033-2220); it is exported so that the
+ * decomposition can be tested without GPUs. */
+ROCFFT_EXPORT rocfft_status b200fft_slab_exchange_offsets(int     ranks,
+                                                          int     chunks,
+                                                          size_t  slab_bytes,
+                                                          int     first,
+                                                          int     chunk,
+                                                          size_t* send_off,
+                                                          size_t* recv_off,
+                                                          size_t* block_bytes);
+
 /* Number of GPU kernels this library has launched in the calling process. */
 ROCFFT_EXPORT unsigned long long b200fft_launch_count();
 

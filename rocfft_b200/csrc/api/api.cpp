@@ -665,6 +665,21 @@ ROCFFT_EXPORT rocfft_status b200fft_plan_describe(const rocfft_plan plan, char* 
     return rocfft_status_success;
 }
 
+ROCFFT_EXPORT rocfft_status b200fft_slab_exchange_offsets(int     ranks,
+                                                          int     chunks,
+                                                          size_t  slab_bytes,
+                                                          int     first,
+                                                          int     chunk,
+                                                          size_t* send_off,
+                                                          size_t* recv_off,
+                                                          size_t* block_bytes)
+{
+    if(ranks < 1 || chunks < 1 || chunk < 0 || chunk >= chunks || !send_off || !recv_off || !block_bytes)
+        return rocfft_status_invalid_arg_value;
+    b200fft::slab_exchange_offsets(ranks, chunks, slab_bytes, first, chunk, send_off, recv_off, block_bytes);
+    return rocfft_status_success;
+}
+
 ROCFFT_EXPORT rocfft_status b200fft_nccl_unique_id(void* id128)
 {
     return b200fft::nccl_unique_id(id128) == 0 ? rocfft_status_success : rocfft_status_failure;

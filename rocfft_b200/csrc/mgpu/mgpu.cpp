@@ -126,6 +126,33 @@ namespace b200fft
         }
     }
 
+    // Byte offsets of the blocks one rank sends and receives in one chunk of one
+    // exchange.  Offsets are relative to the send buffer S and to the receive
+    // buffer (R for the first exchange, the staging buffer R2 for the second).
+    //   first exchange : block for rank q starts at S + c*chunk + q*blk; the block
+    //                    from rank q lands at R + (q*chunks + c)*blk, which places
+    //                    its planes at z = q*lz + c*cz of T[z][y_local][x];
+    //   second exchange: send as above; the block from rank q lands at
+    //                    R2 + c*chunk + q*blk, i.e. R2_c[q][z_local][yc][x].
+    void slab_exchange_offsets(int     ranks,
+                               int     chunks,
+                               size_t  slab_bytes,
+                               int     first,
+                               int     c,
+                               size_t* send_off,
+                               size_t* recv_off,
+                               size_t* block_bytes)
+    {
+        const size_t chunk_bytes = slab_bytes / (size_t)chunks;
+        const size_t blk         = chunk_bytes / (size_t)ranks;
+        *block_bytes             = blk;
+        for(int q = 0; q < ranks; ++q)
+        {
+            send_off[q] = (size_t)c * chunk_bytes + (size_t)q * blk;
+            recv_off[q] = first ? ((size_t)q * chunks + c) * blk : (size_t)c * chunk_bytes + (size_t)q * blk;
+        }
+    }
+
     void build_multi_device_plan(rocfft_plan_t* plan)
     {
         const auto& d = plan->desc;
@@ -385,27 +412,21 @@ namespace b200fft
         cudaStream_t cs   = info->stream; // compute
         cudaStream_t ns   = sp->comm_stream; // NCCL
         const int    k = sp->chunks, P = sp->P;
-        const size_t chunk_bytes = sp->slab_bytes / k;
-        const size_t blkA = chunk_bytes / P; // bytes per destination per chunk (both exchanges)
-
         // the exchange stream must not run ahead of work already queued on the caller's stream
         cudaEventRecord(sp->ev_start, cs);
         cudaStreamWaitEvent(ns, sp->ev_start, 0);
 
+        std::vector<size_t> soff(P), roff(P);
         auto exchange = [&](const char* send_base, char* recv_base, bool first, int c) -> bool {
+            size_t blk = 0;
+            slab_exchange_offsets(P, k, sp->slab_bytes, first ? 1 : 0, c, soff.data(), roff.data(), &blk);
             if(N.GroupStart() != ncclSuccess)
                 return false;
             for(int q = 0; q < P; ++q)
             {
-                const char* sptr = send_base + (size_t)q * blkA;
-                char*       rptr;
-                if(first) // source q fills T[z = q*lz + c*cz ...]: blocks ordered by (q, chunk)
-                    rptr = recv_base + ((size_t)q * k + c) * blkA;
-                else // staging R2_c[q][z_local][yc][x]
-                    rptr = recv_base + (size_t)q * blkA;
-                if(N.Send(sptr, blkA, ncclChar, q, sp->comm, ns) != ncclSuccess)
+                if(N.Send(send_base + soff[q], blk, ncclChar, q, sp->comm, ns) != ncclSuccess)
                     return false;
-                if(N.Recv(rptr, blkA, ncclChar, q, sp->comm, ns) != ncclSuccess)
+                if(N.Recv(recv_base + roff[q], blk, ncclChar, q, sp->comm, ns) != ncclSuccess)
                     return false;
             }
             return N.GroupEnd() == ncclSuccess;
@@ -419,7 +440,7 @@ namespace b200fft
                 return st;
             cudaEventRecord(sp->evA[c], cs);
             cudaStreamWaitEvent(ns, sp->evA[c], 0);
-            if(!exchange(work + sp->off_s + c * chunk_bytes, work + sp->off_r, true, c))
+            if(!exchange(work + sp->off_s, work + sp->off_r, true, c))
                 return rocfft_status_failure;
         }
         cudaEventRecord(sp->ev_all, ns);
@@ -432,7 +453,7 @@ namespace b200fft
                 return st;
             cudaEventRecord(sp->evB[c], cs);
             cudaStreamWaitEvent(ns, sp->evB[c], 0);
-            if(!exchange(work + sp->off_s + c * chunk_bytes, work + sp->off_r2 + c * chunk_bytes, false, c))
+            if(!exchange(work + sp->off_s, work + sp->off_r2, false, c))
                 return rocfft_status_failure;
             cudaEventRecord(sp->evX[c], ns);
         }

@@ -20,6 +20,16 @@ namespace b200fft
                                             void* const*                   out,
                                             const rocfft_execution_info_t* info);
 
+    // schedule of one chunk of one exchange (pure host arithmetic; see mgpu.cpp)
+    void slab_exchange_offsets(int     ranks,
+                               int     chunks,
+                               size_t  slab_bytes,
+                               int     first,
+                               int     c,
+                               size_t* send_off,
+                               size_t* recv_off,
+                               size_t* block_bytes);
+
     // NCCL communicator helpers (0 on success)
     int nccl_unique_id(void* out128);
     int nccl_comm_create(int nranks, int rank, const void* id128, void** comm_out);
