@@ -169,6 +169,12 @@ namespace
         {"row_tma", 10, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
         {"row_r2c_tma", 11, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
         {"row_c2r_tma", 12, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        // paired-column kernels (stockham_colpair.cuh), single precision only
+        {"col_pair", 13, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
+        {"col_pair_blk", 14, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
+        // persistent full-line column kernels (stockham_colwide.cuh)
+        {"col_wide", 15, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
+        {"col_wide_blk", 16, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
     };
     const int kTmaStages = 3;
     // padded lengths M with a single-kernel Bluestein: 2^k, 3*2^k, 5*2^k
@@ -277,6 +283,20 @@ int main(int argc, char** argv)
                     continue;
                 if(n > 4096 && v.id != 0 && v.id != 1 && v.id != 9)
                     continue; // long lengths: plain row kernels and Bluestein only
+                const bool pairv = v.id == 13 || v.id == 14;
+                if(pairv && (prec != 0 || ch.f.size() < 2 || n < 32))
+                    continue;
+                const bool widev = v.id == 15 || v.id == 16;
+                if(widev && (tuned || ch.f.size() < 2 || n < 32 || tpt * 8 > 1024 || ch.f[0] != ept))
+                    continue;
+                if(widev)
+                {
+                    bool all_divide = true;
+                    for(int f : ch.f)
+                        all_divide = all_divide && (ept % f == 0);
+                    if(!all_divide)
+                        continue;
+                }
                 const bool tma = v.id >= 10 && v.id <= 12;
                 if(tma && (ch.f.size() < 2 || n < 16))
                     continue;
@@ -331,10 +351,23 @@ int main(int argc, char** argv)
                     if(2 * (sm + 1024) > 226 * 1024)
                         continue; // fewer than two resident CTAs: the plain kernel does better
                 }
-                if(sm > smem_cap)
+                if(pairv)
+                {
+                    if(tpb < 2 || tpb % 2)
+                        continue;
+                    sm = (size_t)(n + (n >> 4) + 1) * (tpb / 2) * 16;
+                }
+                if(widev)
+                {
+                    tpb = 128 / esz;
+                    sm  = (size_t)n * 128 + (size_t)(n + (n >> 4) + 1) * 64;
+                    if(sm > 225 * 1024)
+                        continue;
+                }
+                else if(sm > smem_cap)
                     continue;
-                const int threads = tpt * tpb;
-                int       minb    = std::max(1, 65536 / (threads * regcap));
+                const int threads = widev ? tpt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
+                int       minb    = std::max(1, 65536 / (threads * (pairv ? 128 : regcap)));
                 if(sm)
                     minb = std::min<int>(minb, (int)(200 * 1024 / (sm + 1024)));
                 minb = std::max(1, std::min(minb, 2048 / threads));
@@ -379,7 +412,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -392,6 +425,10 @@ int main(int argc, char** argv)
             o << "launch_bluestein_kernel<" << k.cfg << ">";
         else if(k.variant >= 10 && k.variant <= 12)
             o << "launch_rows_tma_kernel<" << k.cfg << ", " << (k.variant - 10) << ", " << kTmaStages << ">";
+        else if(k.variant == 13 || k.variant == 14)
+            o << "launch_colpair_kernel<" << k.cfg << ", " << (k.variant == 14 ? "true" : "false") << ">";
+        else if(k.variant == 15 || k.variant == 16)
+            o << "launch_colwide_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ">";
         else
             o << "launch_tile_kernel<" << k.cfg << ">";
         o << "(*a, ntiles, s);\n}\n\n";
@@ -408,7 +445,12 @@ int main(int argc, char** argv)
         for(const Kernel& k : kernels)
         {
             o << "    {" << k.n << ", " << k.prec << ", " << k.variant << ", " << k.tpt << ", " << k.tpb
-              << ", " << k.tpt * k.tpb << ", " << k.f.size() << ", {";
+              << ", "
+              << ((k.variant == 15 || k.variant == 16)   ? k.tpt * 8
+                  : (k.variant == 13 || k.variant == 14) ? k.tpt * k.tpb / 2
+                                                         : k.tpt * k.tpb)
+              << ", " << k.f.size()
+              << ", {";
             for(size_t i = 0; i < 8; ++i)
                 o << (i ? "," : "") << (i < k.f.size() ? k.f[i] : 0);
             o << "}, " << k.smem << "ull, b200fft_launch_" << k.name << ", \"" << k.name << "\"},\n";

@@ -35,6 +35,14 @@ typedef enum b200fft_variant
     B200FFT_ROW_TMA     = 10,
     B200FFT_ROW_R2C_TMA = 11,
     B200FFT_ROW_C2R_TMA = 12,
+    // single-precision column tiles with two adjacent columns per thread (128-bit accesses);
+    // need even strides, an even column count and 16-byte aligned bases
+    B200FFT_COL_PAIR     = 13,
+    B200FFT_COL_PAIR_BLK = 14,
+    // persistent column kernels with 128-byte-wide tiles and asynchronous prefetch
+    // (stockham_colwide.cuh); column count must be a multiple of the tile width
+    B200FFT_COL_WIDE     = 15,
+    B200FFT_COL_WIDE_BLK = 16,
 } b200fft_variant;
 
 typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);

@@ -447,6 +447,58 @@ namespace b200fft
                 };
                 set_blk(a.out, s.out_blk, s.out_bs);
                 fill_outer(o, a, st.loops);
+                // column tiles: the persistent full-line kernel when the layout allows it
+                bool wide_chosen = false;
+                // (measured slower than the alternatives on B200 so far: one CTA per SM moves in
+                // lock step through its phases; opt-in until that is fixed)
+                if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK) && getenv("ROCFFT_B200_COLWIDE"))
+                {
+                    const b200fft_pool_entry* wk = pool_find(
+                        s.n, prec_, kern->variant == B200FFT_COL_STR ? B200FFT_COL_WIDE : B200FFT_COL_WIDE_BLK);
+                    const long long al = prec_ == 0 ? 2 : 1; // strides must be multiples of 16 bytes
+                    bool ok = wk && st.loops.empty() && (a.on[0] % wk->tpb == 0) && (a.in.es % al == 0)
+                              && (a.out.es % al == 0) && (a.out.bs % al == 0) && a.in.os[0] == 1 && a.out.os[0] == 1
+                              && (s.in.byte_off[0] % 16 == 0) && (s.out.byte_off[0] % 16 == 0);
+                    for(int k = 1; k < 3; ++k)
+                        ok = ok && (a.in.os[k] % al == 0) && (a.out.os[k] % al == 0);
+                    ok = ok && (long long)s.n * std::llabs(a.in.es) < (1ll << 31)
+                         && (long long)s.n * std::llabs(a.out.es) < (1ll << 31);
+                    if(ok)
+                    {
+                        st.kern_unaligned   = kern;
+                        st.ntile0_unaligned = (a.on[0] + kern->tpb - 1) / kern->tpb;
+                        st.ntiles_unaligned = (unsigned long long)st.ntile0_unaligned * a.on[1] * a.on[2];
+                        kern                = wk;
+                        st.kern             = wk;
+                        wide_chosen         = true;
+                    }
+                }
+                // single-precision column tiles: two columns per thread when everything is even
+                if(!wide_chosen && (kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK) && prec_ == 0
+                   && !getenv("ROCFFT_B200_NO_COLPAIR"))
+                {
+                    const b200fft_pool_entry* pk = pool_find(
+                        s.n, prec_, kern->variant == B200FFT_COL_STR ? B200FFT_COL_PAIR : B200FFT_COL_PAIR_BLK);
+                    bool even = pk && st.loops.empty() && (a.on[0] % 2 == 0) && (a.in.es % 2 == 0) && (a.out.es % 2 == 0)
+                                && (a.out.bs % 2 == 0) && a.in.os[0] == 1 && a.out.os[0] == 1
+                                && (s.in.byte_off[0] % 16 == 0) && (s.out.byte_off[0] % 16 == 0);
+                    for(int k = 1; k < 3; ++k)
+                        even = even && (a.in.os[k] % 2 == 0) && (a.out.os[k] % 2 == 0);
+                    // 32-bit offsets inside one transform
+                    even = even && (long long)s.n * std::llabs(a.in.es) < (1ll << 31)
+                           && (long long)s.n * std::llabs(a.out.es) < (1ll << 31);
+                    // measured: with row pitches of megabytes the plain kernel (more threads in
+                    // flight per tile) is faster; the paired kernel wins at moderate pitches
+                    even = even && std::llabs(a.in.es) * 8 <= (256ll << 10);
+                    if(even)
+                    {
+                        st.kern_unaligned   = kern;
+                        st.ntile0_unaligned = (a.on[0] + kern->tpb - 1) / kern->tpb;
+                        st.ntiles_unaligned = (unsigned long long)st.ntile0_unaligned * a.on[1] * a.on[2];
+                        kern                = pk;
+                        st.kern             = pk;
+                    }
+                }
                 // contiguous rows: prefer the persistent TMA-pipelined kernel
                 {
                     int tma_variant = -1;
