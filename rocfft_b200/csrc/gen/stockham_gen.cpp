@@ -175,6 +175,9 @@ namespace
         // persistent full-line column kernels (stockham_colwide.cuh)
         {"col_wide", 15, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
         {"col_wide_blk", 16, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
+        // cluster-of-two column kernels (stockham_colcluster.cuh)
+        {"col_cl", 17, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
+        {"col_cl_blk", 18, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
     };
     const int kTmaStages = 3;
     // padded lengths M with a single-kernel Bluestein: 2^k, 3*2^k, 5*2^k
@@ -286,7 +289,10 @@ int main(int argc, char** argv)
                 const bool pairv = v.id == 13 || v.id == 14;
                 if(pairv && (prec != 0 || ch.f.size() < 2 || n < 32))
                     continue;
-                const bool widev = v.id == 15 || v.id == 16;
+                const bool clv   = v.id == 17 || v.id == 18;
+                if(clv && ((n & (n - 1)) != 0 || n < 64 || tpt % 2))
+                    continue;
+                const bool widev = v.id == 15 || v.id == 16 || clv;
                 if(widev && (tuned || ch.f.size() < 2 || n < 32 || tpt * 8 > 1024 || ch.f[0] != ept))
                     continue;
                 if(widev)
@@ -357,7 +363,14 @@ int main(int argc, char** argv)
                         continue;
                     sm = (size_t)(n + (n >> 4) + 1) * (tpb / 2) * 16;
                 }
-                if(widev)
+                if(clv)
+                {
+                    tpb = 128 / esz;
+                    sm  = (size_t)(n / 2 + (n >> 5) + 1) * 128;
+                    if(sm > 200 * 1024 || tpt * 4 > 1024)
+                        continue;
+                }
+                else if(widev)
                 {
                     tpb = 128 / esz;
                     sm  = (size_t)n * 128 + (size_t)(n + (n >> 4) + 1) * 64;
@@ -366,8 +379,8 @@ int main(int argc, char** argv)
                 }
                 else if(sm > smem_cap)
                     continue;
-                const int threads = widev ? tpt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
-                int       minb    = std::max(1, 65536 / (threads * (pairv ? 128 : regcap)));
+                const int threads = clv ? tpt * 4 : widev ? tpt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
+                int       minb    = std::max(1, 65536 / (threads * ((pairv || clv) ? 128 : regcap)));
                 if(sm)
                     minb = std::min<int>(minb, (int)(200 * 1024 / (sm + 1024)));
                 minb = std::max(1, std::min(minb, 2048 / threads));
@@ -412,7 +425,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\n#include \"stockham_colcluster.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -429,6 +442,8 @@ int main(int argc, char** argv)
             o << "launch_colpair_kernel<" << k.cfg << ", " << (k.variant == 14 ? "true" : "false") << ">";
         else if(k.variant == 15 || k.variant == 16)
             o << "launch_colwide_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ">";
+        else if(k.variant == 17 || k.variant == 18)
+            o << "launch_colcluster_kernel<" << k.cfg << ", 2, " << (k.variant == 18 ? "true" : "false") << ">";
         else
             o << "launch_tile_kernel<" << k.cfg << ">";
         o << "(*a, ntiles, s);\n}\n\n";
@@ -446,7 +461,8 @@ int main(int argc, char** argv)
         {
             o << "    {" << k.n << ", " << k.prec << ", " << k.variant << ", " << k.tpt << ", " << k.tpb
               << ", "
-              << ((k.variant == 15 || k.variant == 16)   ? k.tpt * 8
+              << ((k.variant == 17 || k.variant == 18)   ? k.tpt * 4
+                  : (k.variant == 15 || k.variant == 16) ? k.tpt * 8
                   : (k.variant == 13 || k.variant == 14) ? k.tpt * k.tpb / 2
                                                          : k.tpt * k.tpb)
               << ", " << k.f.size()

@@ -245,9 +245,38 @@ namespace b200fft
                 const int k = b % CH;
                 if constexpr(P > 0)
                 {
+                    // Long transforms: the stacked table no longer fits the L1 left beside the
+                    // shared tile, so twiddle loads come from L2.  Load only the legs j = 1,2,3 and
+                    // j = 4a and form the others as products (j = 4a + b): 6 instead of 15 loads
+                    // for radix 16, 10 instead of 31 for radix 32, at the cost of one complex
+                    // multiply per remaining leg (error of one extra rounding, far inside the bound).
+                    constexpr bool TW4 = (C::N >= 8192) && (W >= 8);
+                    if constexpr(TW4)
+                    {
+                        T2 wb[3];
 #pragma unroll
-                    for(int j = 1; j < W; ++j)
-                        x[i][j] = cmul(x[i][j], tw[TWO + (j - 1) * CH + k]);
+                        for(int b4 = 1; b4 < 4; ++b4)
+                        {
+                            wb[b4 - 1] = tw[TWO + (b4 - 1) * CH + k];
+                            x[i][b4]   = cmul(x[i][b4], wb[b4 - 1]);
+                        }
+#pragma unroll
+                        for(int a4 = 1; 4 * a4 < W; ++a4)
+                        {
+                            const T2 wa = tw[TWO + (4 * a4 - 1) * CH + k];
+                            x[i][4 * a4] = cmul(x[i][4 * a4], wa);
+#pragma unroll
+                            for(int b4 = 1; b4 < 4; ++b4)
+                                if(4 * a4 + b4 < W)
+                                    x[i][4 * a4 + b4] = cmul(x[i][4 * a4 + b4], cmul(wa, wb[b4 - 1]));
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for(int j = 1; j < W; ++j)
+                            x[i][j] = cmul(x[i][j], tw[TWO + (j - 1) * CH + k]);
+                    }
                 }
                 Butterfly<W, T2>::run(x[i]);
                 const int base = (b / CH) * (W * CH) + k;

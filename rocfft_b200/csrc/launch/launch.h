@@ -43,6 +43,10 @@ typedef enum b200fft_variant
     // (stockham_colwide.cuh); column count must be a multiple of the tile width
     B200FFT_COL_WIDE     = 15,
     B200FFT_COL_WIDE_BLK = 16,
+    // 128-byte-wide column tiles shared by a cluster of two CTAs through distributed shared
+    // memory (stockham_colcluster.cuh); power-of-two lengths
+    B200FFT_COL_CL     = 17,
+    B200FFT_COL_CL_BLK = 18,
 } b200fft_variant;
 
 typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);

@@ -449,12 +449,19 @@ namespace b200fft
                 fill_outer(o, a, st.loops);
                 // column tiles: the persistent full-line kernel when the layout allows it
                 bool wide_chosen = false;
-                // (measured slower than the alternatives on B200 so far: one CTA per SM moves in
-                // lock step through its phases; opt-in until that is fixed)
-                if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK) && getenv("ROCFFT_B200_COLWIDE"))
+                // Two full-line designs exist: a persistent one-CTA-per-SM kernel (ROCFFT_B200_COLWIDE)
+                // and a cluster-of-two kernel over distributed shared memory (ROCFFT_B200_COLCLUSTER).
+                // Both measured slower than the 64-byte-tile kernels on B200 so far (too few warps
+                // in flight per SM), so they are opt-in.
+                if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
+                   && (getenv("ROCFFT_B200_COLWIDE") || getenv("ROCFFT_B200_COLCLUSTER")))
                 {
+                    const bool use_wide = getenv("ROCFFT_B200_COLWIDE") != nullptr;
                     const b200fft_pool_entry* wk = pool_find(
-                        s.n, prec_, kern->variant == B200FFT_COL_STR ? B200FFT_COL_WIDE : B200FFT_COL_WIDE_BLK);
+                        s.n,
+                        prec_,
+                        kern->variant == B200FFT_COL_STR ? (use_wide ? B200FFT_COL_WIDE : B200FFT_COL_CL)
+                                                         : (use_wide ? B200FFT_COL_WIDE_BLK : B200FFT_COL_CL_BLK));
                     const long long al = prec_ == 0 ? 2 : 1; // strides must be multiples of 16 bytes
                     bool ok = wk && st.loops.empty() && (a.on[0] % wk->tpb == 0) && (a.in.es % al == 0)
                               && (a.out.es % al == 0) && (a.out.bs % al == 0) && a.in.os[0] == 1 && a.out.os[0] == 1
