@@ -29,6 +29,11 @@ typedef struct b200fft_ioview
     unsigned  blk_mul; // ceil(2^32 / blk), for an exact multiply-high division
     int       pad_;
     long long bs;
+    // Optional table with one base pointer per block (blocked-output variants): block q is
+    // written at blk_ptrs[q] instead of p[0] + q * bs.  The multi-device layer points the
+    // entries at peer GPUs' receive buffers, so the FFT pass stores its result straight
+    // into the other ranks' memory over NVLink.
+    void* const* blk_ptrs;
 } b200fft_ioview;
 
 // Arguments of every Stockham tile kernel.

@@ -126,6 +126,7 @@ namespace b200fft
                                                     typename C::T2 (&r)[ColCluster<C, CL>::VEC][ColCluster<C, CL>::EPT],
                                                     const b200fft_ioview&      out,
                                                     typename C::T2*            gout,
+                                                    const long long            obase,
                                                     typename C::T              sx,
                                                     typename C::T              sy)
     {
@@ -154,7 +155,7 @@ namespace b200fft
 #pragma unroll
                     for(int v = 0; v < CC::VEC; ++v)
                         tmp[v] = r[v][i * PP::W + j];
-                    T2* dst = BLK ? gout + elem_offset(out, e0 + j * PP::CH) : q + j * ost;
+                    T2* dst = BLK ? blk_address<T2>(out, obase, e0 + j * PP::CH) : q + j * ost;
                     *reinterpret_cast<U*>(dst) = Unit16<T>::pack(tmp, sx, sy);
                 }
             }
@@ -204,7 +205,7 @@ namespace b200fft
             }
             // nobody may overwrite (or leave) before both CTAs have finished reading
             ptx::cluster_sync();
-            colcluster_from<C, CL, P + 1, BLK>(rank, tl, u, sm, win, tw, r, out, gout, sx, sy);
+            colcluster_from<C, CL, P + 1, BLK>(rank, tl, u, sm, win, tw, r, out, gout, obase, sx, sy);
         }
     }
 
@@ -263,7 +264,7 @@ namespace b200fft
                     r[v][j] = tmp[v];
             }
         }
-        colcluster_from<C, CL, 0, BLK>(rank, tl, u, sm, win, tw, r, a.out, gout, sx, sy);
+        colcluster_from<C, CL, 0, BLK>(rank, tl, u, sm, win, tw, r, a.out, gout, obase, sx, sy);
     }
 
     template <class C, int CL, bool BLK>

@@ -237,7 +237,7 @@ namespace b200fft
 #pragma unroll
                         for(int j = 0; j < PP::W; ++j)
                         {
-                            float2* dst = BLK ? gout + elem_offset(a.out, e0 + j * PP::CH) : q + j * ost;
+                            float2* dst = BLK ? blk_address<float2>(a.out, obase, e0 + j * PP::CH) : q + j * ost;
                             *reinterpret_cast<float4*>(dst)
                                 = make_float4(xa[i][j].x * sx, xa[i][j].y * sy, xb[i][j].x * sx, xb[i][j].y * sy);
                         }

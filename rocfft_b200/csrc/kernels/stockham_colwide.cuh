@@ -211,6 +211,7 @@ namespace b200fft
                                                  typename C::T2 (&r)[ColWide<C>::VEC][C::N / C::TPT],
                                                  const b200fft_ioview&   out,
                                                  typename C::T2*         gout,
+                                                 const long long         obase,
                                                  typename C::T           sx,
                                                  typename C::T           sy)
     {
@@ -236,7 +237,7 @@ namespace b200fft
 #pragma unroll
                     for(int v = 0; v < CW::VEC; ++v)
                         tmp[v] = r[v][i * PP::W + j];
-                    T2* dst = BLK ? gout + elem_offset(out, e0 + j * PP::CH) : q + j * ost;
+                    T2* dst = BLK ? blk_address<T2>(out, obase, e0 + j * PP::CH) : q + j * ost;
                     *reinterpret_cast<typename CW::U*>(dst) = Unit16<T>::pack(tmp, sx, sy);
                 }
             }
@@ -244,7 +245,7 @@ namespace b200fft
         else
         {
             colwide_exchange<C, P>(t, u, xch, r);
-            colwide_from<C, P + 1, BLK>(t, u, xch, tw, r, out, gout, sx, sy);
+            colwide_from<C, P + 1, BLK>(t, u, xch, tw, r, out, gout, obase, sx, sy);
         }
     }
 
@@ -320,7 +321,7 @@ namespace b200fft
             const TilePos   tp    = decode_tile(a, (unsigned)tile, CW::COLS);
             const long long obase = view_base(a.out, tp.i0_first + u * CW::VEC, tp.i1, tp.i2);
             T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
-            colwide_from<C, 0, BLK>(t, u, xch, tw, x, a.out, gout, sx, sy);
+            colwide_from<C, 0, BLK>(t, u, xch, tw, x, a.out, gout, obase, sx, sy);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     }

@@ -135,6 +135,18 @@ namespace b200fft
         return (long long)q * v.bs + (long long)r * v.es;
     }
 
+    // address of point e of a blocked output: either inside the local buffer or, with a
+    // per-block pointer table, inside the buffer of the rank that owns the block
+    template <typename T2>
+    __device__ __forceinline__ T2* blk_address(const b200fft_ioview& v, long long base, int e)
+    {
+        const unsigned q = __umulhi((unsigned)e, v.blk_mul);
+        const unsigned r = (unsigned)e - q * v.blk;
+        if(v.blk_ptrs)
+            return reinterpret_cast<T2*>(v.blk_ptrs[q]) + base + (long long)r * v.es;
+        return reinterpret_cast<T2*>(v.p[0]) + base + (long long)q * v.bs + (long long)r * v.es;
+    }
+
     template <class C>
     __device__ __forceinline__ typename C::T2
         gload(const b200fft_ioview& v, long long base, int e, bool inverse)
@@ -192,7 +204,7 @@ namespace b200fft
         }
         else if constexpr(C::IOKO == IO_BLKOUT)
         {
-            reinterpret_cast<T2*>(v.p[0])[base + elem_offset(v, e)] = val;
+            *blk_address<T2>(v, base, e) = val;
         }
         else
         {

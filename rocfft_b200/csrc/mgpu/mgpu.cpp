@@ -21,9 +21,15 @@
 //               outer strides and writes the caller's slab in natural order.
 //     Three HBM round trips per rank in total, the minimum for a 3D transform
 //     without on-chip plane residency.
-//   * The work is cut into chunks; chunk c+1 is transformed while chunk c is on
-//     the wire (compute on the caller's stream, NCCL on an internal stream,
-//     events in between).
+//   * Default exchange: none as a separate step.  The receive buffers belong to the
+//     plan and are mapped into every rank with CUDA IPC; passes A and B get a table
+//     of per-destination base pointers and store each block straight into the owning
+//     rank's buffer over NVLink while they compute (plain peer stores: no multimem, no
+//     TMA).  A one-word NCCL all-reduce on the caller's stream is the barrier between
+//     phases.  The plan then needs no caller work buffer.
+//   * ROCFFT_B200_MGPU_NCCL=1 selects NCCL grouped send/recv instead: the work is
+//     cut into chunks; chunk c+1 is transformed while chunk c is on the wire (compute
+//     on the caller's stream, NCCL on an internal stream, events in between).
 #include "mgpu.h"
 #include "../plan/planner_impl.h"
 #include <cstdio>
@@ -51,6 +57,8 @@ namespace b200fft
             ncclResult_t (*GroupStart)()                                                         = nullptr;
             ncclResult_t (*GroupEnd)()                                                           = nullptr;
             ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t)
+                = nullptr;
+            ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t)
                 = nullptr;
             const char* (*GetErrorString)(ncclResult_t) = nullptr;
             bool ok                                     = false;
@@ -80,9 +88,10 @@ namespace b200fft
                 api.GroupStart     = (decltype(api.GroupStart))sym("ncclGroupStart");
                 api.GroupEnd       = (decltype(api.GroupEnd))sym("ncclGroupEnd");
                 api.AllGather      = (decltype(api.AllGather))sym("ncclAllGather");
+                api.AllReduce      = (decltype(api.AllReduce))sym("ncclAllReduce");
                 api.GetErrorString = (decltype(api.GetErrorString))sym("ncclGetErrorString");
                 api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.CommCount && api.CommUserRank
-                         && api.Send && api.Recv && api.GroupStart && api.GroupEnd && api.AllGather;
+                         && api.Send && api.Recv && api.GroupStart && api.GroupEnd && api.AllGather && api.AllReduce;
             });
             return api;
         }
@@ -114,6 +123,13 @@ namespace b200fft
             std::vector<cudaEvent_t> evA, evB, evX;
             cudaEvent_t              ev_all = nullptr, ev_start = nullptr;
             int                      device  = 0;
+            // peer-to-peer mode: the FFT passes store straight into the other ranks' receive
+            // buffers (plan-owned, shared through CUDA IPC); NCCL only provides the barriers
+            bool               p2p = false;
+            void *             R = nullptr, *R2 = nullptr; // this rank's receive buffers
+            std::vector<void*> peer_r, peer_r2; // every rank's buffers as mapped here
+            void **            tab_a = nullptr, **tab_b = nullptr; // device tables of block bases
+            int*               bar   = nullptr; // device words for the barrier all-reduce
         };
 
         size_t total_work(const SlabPlan& sp)
@@ -229,12 +245,18 @@ namespace b200fft
                     throw std::runtime_error("ranks disagree on the slab layout");
         }
 
-        // chunking for overlap of compute and exchange
+        // Exchange mode.  Default: peer-to-peer stores from inside the FFT kernels.
+        // ROCFFT_B200_MGPU_NCCL=1 selects the NCCL send/recv exchange instead.
+        sp->p2p = getenv("ROCFFT_B200_MGPU_NCCL") == nullptr;
+
+        // chunking for overlap of compute and exchange (NCCL mode only)
         int k = 4;
         if(const char* env = getenv("ROCFFT_B200_MGPU_CHUNKS"))
             k = std::max(1, atoi(env));
         while(k > 1 && (sp->lz % k || sp->ly % k))
             k /= 2;
+        if(sp->p2p)
+            k = 1;
         sp->chunks = k;
 
         const size_t nx = sp->nx, ny = sp->ny, lz = sp->lz, ly = sp->ly;
@@ -265,6 +287,78 @@ namespace b200fft
         S.id = R.id = R2.id = BUF_TEMP;
         const size_t chunk_bytes = sp->slab_bytes / k;
 
+        if(sp->p2p)
+        {
+            // Plan-owned receive buffers, visible to every rank through CUDA IPC.
+            int ndev = 0;
+            if(cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+                sp->p2p = false; // no GPU in this process: the plan stays inspectable only
+        }
+        if(sp->p2p)
+        {
+            if(cudaMalloc(&sp->R, sp->slab_bytes) != cudaSuccess || cudaMalloc(&sp->R2, sp->slab_bytes) != cudaSuccess)
+                throw std::runtime_error("exchange buffer allocation failed");
+            sp->peer_r.assign(P, nullptr);
+            sp->peer_r2.assign(P, nullptr);
+            if(P == 1)
+            {
+                sp->peer_r[0]  = sp->R;
+                sp->peer_r2[0] = sp->R2;
+            }
+            else
+            {
+                cudaIpcMemHandle_t mine[2];
+                if(cudaIpcGetMemHandle(&mine[0], sp->R) != cudaSuccess
+                   || cudaIpcGetMemHandle(&mine[1], sp->R2) != cudaSuccess)
+                    throw std::runtime_error("cudaIpcGetMemHandle failed");
+                char* dbuf = nullptr;
+                if(cudaMalloc(&dbuf, sizeof(mine) * (P + 1)) != cudaSuccess)
+                    throw std::runtime_error("cudaMalloc failed");
+                cudaMemcpy(dbuf, mine, sizeof mine, cudaMemcpyHostToDevice);
+                ncclResult_t r = N.AllGather(dbuf, dbuf + sizeof(mine), sizeof mine, ncclChar, sp->comm, nullptr);
+                cudaError_t  e = cudaStreamSynchronize(nullptr);
+                std::vector<cudaIpcMemHandle_t> all(2 * P);
+                cudaMemcpy(all.data(), dbuf + sizeof(mine), sizeof(mine) * P, cudaMemcpyDeviceToHost);
+                cudaFree(dbuf);
+                nccl_check(r, "ncclAllGather");
+                if(e != cudaSuccess)
+                    throw std::runtime_error("IPC handle exchange failed");
+                for(int q = 0; q < P; ++q)
+                {
+                    if(q == sp->rank)
+                    {
+                        sp->peer_r[q]  = sp->R;
+                        sp->peer_r2[q] = sp->R2;
+                        continue;
+                    }
+                    if(cudaIpcOpenMemHandle(&sp->peer_r[q], all[2 * q], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess
+                       || cudaIpcOpenMemHandle(&sp->peer_r2[q], all[2 * q + 1], cudaIpcMemLazyEnablePeerAccess)
+                              != cudaSuccess)
+                        throw std::runtime_error("cudaIpcOpenMemHandle failed (peer access between the GPUs is required)");
+                }
+            }
+            // block q of pass A lands in rank q's T at planes z = rank*lz ..., block q of pass B in
+            // rank q's staging buffer at part `rank`; both are rank * (slab / P) bytes into the buffer
+            const size_t       part = sp->slab_bytes / P;
+            std::vector<void*> ta(P), tb(P);
+            for(int q = 0; q < P; ++q)
+            {
+                ta[q] = static_cast<char*>(sp->peer_r[q]) + (size_t)sp->rank * part;
+                tb[q] = static_cast<char*>(sp->peer_r2[q]) + (size_t)sp->rank * part;
+            }
+            if(cudaMalloc(&sp->tab_a, sizeof(void*) * P) != cudaSuccess
+               || cudaMalloc(&sp->tab_b, sizeof(void*) * P) != cudaSuccess || cudaMalloc(&sp->bar, 64) != cudaSuccess)
+                throw std::runtime_error("cudaMalloc failed");
+            cudaMemcpy(sp->tab_a, ta.data(), sizeof(void*) * P, cudaMemcpyHostToDevice);
+            cudaMemcpy(sp->tab_b, tb.data(), sizeof(void*) * P, cudaMemcpyHostToDevice);
+            cudaMemset(sp->bar, 0, 64);
+            S.id = R.id = R2.id = BUF_ABS;
+            sp->off_s  = 0;
+            sp->off_r  = reinterpret_cast<size_t>(sp->R);
+            sp->off_r2 = reinterpret_cast<size_t>(sp->R2);
+            sp->work_bytes = 0;
+        }
+
         for(int c = 0; c < k; ++c)
         {
             // ---- pass A: FFT along Y for z-chunk c, slab -> S_c[q][zc][yq][x]
@@ -283,6 +377,8 @@ namespace b200fft
                 s.in.byte_off[0] = c * cz * nx * ny * sp->csize;
                 s.out            = S;
                 s.out.byte_off[0] = sp->off_s + c * chunk_bytes;
+                if(sp->p2p)
+                    s.out_blk_ptrs = sp->tab_a;
                 s.inverse        = inverse;
                 p.emit_c2c_1d(s);
                 sp->passA.push_back(std::move(core));
@@ -303,6 +399,8 @@ namespace b200fft
                 s.in.byte_off[0]  = sp->off_r + c * cy * nx * sp->csize;
                 s.out             = S;
                 s.out.byte_off[0] = sp->off_s + c * chunk_bytes;
+                if(sp->p2p)
+                    s.out_blk_ptrs = sp->tab_b;
                 s.inverse         = inverse;
                 p.emit_c2c_1d(s);
                 sp->passB.push_back(std::move(core));
@@ -331,7 +429,8 @@ namespace b200fft
                 sp->passC.push_back(std::move(core));
             }
         }
-        sp->work_bytes = std::max(sp->work_bytes, total_work(*sp));
+        if(!sp->p2p)
+            sp->work_bytes = std::max(sp->work_bytes, total_work(*sp));
 
         bool host_only = false;
         for(auto* v : {&sp->passA, &sp->passB, &sp->passC})
@@ -370,6 +469,24 @@ namespace b200fft
             cudaEventDestroy(sp->ev_start);
         if(sp->comm_stream)
             cudaStreamDestroy(sp->comm_stream);
+        if(sp->p2p)
+        {
+            // unmap the peers' buffers, then release our own
+            for(int q = 0; q < (int)sp->peer_r.size(); ++q)
+            {
+                if(q == sp->rank)
+                    continue;
+                if(sp->peer_r[q])
+                    cudaIpcCloseMemHandle(sp->peer_r[q]);
+                if(sp->peer_r2[q])
+                    cudaIpcCloseMemHandle(sp->peer_r2[q]);
+            }
+            cudaFree(sp->tab_a);
+            cudaFree(sp->tab_b);
+            cudaFree(sp->bar);
+            cudaFree(sp->R);
+            cudaFree(sp->R2);
+        }
         delete sp;
         plan->mgpu = nullptr;
     }
@@ -403,11 +520,34 @@ namespace b200fft
                                             const rocfft_execution_info_t* info)
     {
         auto* sp = static_cast<SlabPlan*>(plan->mgpu);
-        if(!sp || !sp->comm_stream)
+        if(!sp || (!sp->comm_stream && !sp->p2p))
             return rocfft_status_failure;
         NcclApi& N = nccl();
+        if(sp->p2p)
+        {
+            // Fused compute + exchange: pass A stores every destination's block straight into
+            // that rank's receive buffer over NVLink; a stream-ordered all-reduce of one word is
+            // the barrier that tells every rank its buffer is complete; same for pass B; pass C
+            // is local.  The barrier at the end of a phase also guarantees that nobody still
+            // reads a buffer when the next call (or phase) overwrites it.
+            cudaStream_t s = info->stream;
+            auto barrier = [&](int slot) {
+                return N.AllReduce(sp->bar + slot, sp->bar + 8 + slot, 1, ncclInt, ncclSum, sp->comm, s) == ncclSuccess;
+            };
+            rocfft_status st = execute_core(*sp->passA[0], in, out, nullptr, s);
+            if(st != rocfft_status_success)
+                return st;
+            if(sp->P > 1 && !barrier(0))
+                return rocfft_status_failure;
+            st = execute_core(*sp->passB[0], in, out, nullptr, s);
+            if(st != rocfft_status_success)
+                return st;
+            if(sp->P > 1 && !barrier(1))
+                return rocfft_status_failure;
+            return execute_core(*sp->passC[0], in, out, nullptr, s);
+        }
         if(!info->workBuffer || info->workBufferSize < sp->work_bytes)
-            return rocfft_status_invalid_work_buffer; // multi-device plans need a caller-owned work buffer
+            return rocfft_status_invalid_work_buffer; // the NCCL exchange needs a caller-owned work buffer
         char*        work = static_cast<char*>(info->workBuffer);
         cudaStream_t cs   = info->stream; // compute
         cudaStream_t ns   = sp->comm_stream; // NCCL

@@ -28,6 +28,10 @@ namespace b200fft
             case BUF_USER_OUT:
                 src = out;
                 break;
+            case BUF_ABS:
+                p[0] = reinterpret_cast<void*>(b.byte_off[0]);
+                p[1] = nullptr;
+                return true;
             case BUF_TEMP:
                 if(!work)
                     return false;

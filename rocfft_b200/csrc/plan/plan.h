@@ -58,6 +58,7 @@ namespace b200fft
         BUF_USER_IN  = 0,
         BUF_USER_OUT = 1,
         BUF_TEMP     = 2,
+        BUF_ABS      = 3, // a fixed device address owned by the plan (byte_off[0] holds it)
     };
 
     // where a view's base pointer(s) come from at execute time

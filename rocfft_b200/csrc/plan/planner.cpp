@@ -134,7 +134,7 @@ namespace b200fft
         {
             o << "  [" << i++ << "] " << s.note;
             auto buf = [](const BufRef& b) {
-                const char* names[] = {"in", "out", "temp"};
+                const char* names[] = {"in", "out", "temp", "plan"};
                 return std::string(names[b.id]) + "+" + std::to_string(b.byte_off[0]);
             };
             o << "  " << buf(s.in) << " -> " << buf(s.out);

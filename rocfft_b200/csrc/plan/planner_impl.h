@@ -31,8 +31,9 @@ namespace b200fft
             bool                  use_scale = false;
             double                scale     = 1.0;
             // optional two-level output stride along the transform (see b200fft_ioview::blk)
-            size_t    out_blk = 0;
-            ptrdiff_t out_bs  = 0;
+            size_t       out_blk = 0;
+            ptrdiff_t    out_bs  = 0;
+            void* const* out_blk_ptrs = nullptr; // device table: one base pointer per block
             // fused kernels: a specific pool variant and its extra table
             int         force_variant = -1;
             const void* aux0          = nullptr;
@@ -446,6 +447,7 @@ namespace b200fft
                         v.es = bs; // blocks of one point: a plain stride
                 };
                 set_blk(a.out, s.out_blk, s.out_bs);
+                a.out.blk_ptrs = s.out_blk_ptrs;
                 fill_outer(o, a, st.loops);
                 // column tiles: the persistent full-line kernel when the layout allows it
                 bool wide_chosen = false;
@@ -454,8 +456,11 @@ namespace b200fft
                 // Both measured slower than the 64-byte-tile kernels on B200 so far (too few warps
                 // in flight per SM), so they are opt-in.
                 if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
-                   && (getenv("ROCFFT_B200_COLWIDE") || getenv("ROCFFT_B200_COLCLUSTER")))
+                   && (getenv("ROCFFT_B200_COLWIDE") || getenv("ROCFFT_B200_COLCLUSTER")
+                       || (s.out_blk_ptrs && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
                 {
+                    // stores that cross NVLink want whole 128-byte lines: the cluster kernel is the
+                    // default when the output goes to other ranks' buffers
                     const bool use_wide = getenv("ROCFFT_B200_COLWIDE") != nullptr;
                     const b200fft_pool_entry* wk = pool_find(
                         s.n,

@@ -95,8 +95,9 @@ class SlabFFT3D:
         self._work = None
 
     def attach(self, torch, stream):
-        self._work = torch.empty(self.work_bytes, dtype=torch.uint8, device="cuda")
-        assert rf.rocfft_execution_info_set_work_buffer(self.info, self._work.data_ptr(), self.work_bytes) == 0
+        if self.work_bytes:
+            self._work = torch.empty(self.work_bytes, dtype=torch.uint8, device="cuda")
+            assert rf.rocfft_execution_info_set_work_buffer(self.info, self._work.data_ptr(), self.work_bytes) == 0
         assert rf.rocfft_execution_info_set_stream(self.info, stream) == 0
 
     def execute(self, in_ptr, out_ptr=None):
@@ -203,8 +204,8 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
                 "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": HEADLINE, "lengths": [nx, ny, nz], "decomposition": f"z-slabs x{world}",
-                           "placement": "inplace", "exchange": "NCCL grouped send/recv, 2 global transposes",
-                           "chunks": int(os.environ.get("ROCFFT_B200_MGPU_CHUNKS", "4")),
+                           "placement": "inplace", "exchange": ("NCCL grouped send/recv, 2 global transposes" if os.environ.get("ROCFFT_B200_MGPU_NCCL")
+                                        else "peer stores over NVLink fused into FFT passes A and B, 2 global transposes"),
                            "l2": "slab >> L2, no flush needed"},
                 "roofline": {"bound": "nvlink", "achieved": a2a_bytes / ms_max / 1e6, "peak": 770.0,
                              "peak_source": "measured peer copy per direction", "unit": "GB/s",
