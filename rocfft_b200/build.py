@@ -28,6 +28,8 @@ NVCC = os.path.join(CUDA, "bin", "nvcc")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v",
+              # the pool holds thousands of kernels: compressed fatbins keep the library near 100 MB
+              "-Xfatbin", "-compress-all",
               "-I", os.path.join(CSRC, "kernels"), "-I", os.path.join(CSRC, "launch"), "-I", GEN,
               "-I", INCLUDE]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", INCLUDE, "-I", os.path.join(CUDA, "include"),

@@ -50,19 +50,16 @@ namespace
                 s.insert(n);
             return std::vector<int>(s.begin(), s.end());
         }
-        const int extra[] = {3,   5,   6,   7,   9,   10,  11,  12,  13,  14,  15,  18,  20,   21,
-                             22,  24,  25,  26,  27,  28,  30,  33,  35,  36,  39,  40,  42,   44,
-                             45,  48,  49,  50,  52,  54,  55,  56,  60,  63,  65,  70,  72,   75,
-                             77,  78,  80,  81,  84,  88,  90,  91,  96,  98,  99,  100, 104,  108,
-                             110, 112, 117, 120, 121, 125, 126, 130, 135, 140, 143, 144, 150,  160,
-                             162, 168, 169, 175, 176, 180, 192, 196, 200, 208, 216, 224, 225,  240,
-                             243, 250, 256, 270, 288, 300, 320, 324, 336, 343, 360, 375, 384,  400,
-                             432, 448, 480, 486, 500, 540, 576, 600, 625, 640, 648, 672, 675,  720,
-                             729, 750, 768, 800, 864, 896, 900, 960, 972, 1000, 1080, 1125, 1152, 1200,
-                             1215, 1250, 1280, 1296, 1344, 1350, 1440, 1458, 1500, 1536, 1600, 1620, 1728, 1792,
-                             1800, 1875, 1920, 1944, 2000, 2025, 2160, 2187, 2250, 2304, 2400, 2430, 2500, 2560,
-                             2592, 2700, 2880, 2916, 3000, 3072, 3125, 3200, 3240, 3375, 3456, 3600, 3645, 3750,
-                             3840, 3888, 4000, 4050};
+        const int extra[] = {3,    5,    6,    7,    9,    10,   11,   12,   13,   14,   15,   18,   20,   21,
+                             22,   24,   25,   26,   27,   28,   30,   35,   36,   40,   42,   45,   48,   49,
+                             50,   54,   56,   60,   63,   70,   72,   75,   80,   81,   84,   90,   96,   98,
+                             100,  108,  112,  120,  121,  125,  126,  135,  140,  144,  150,  160,  162,  168,
+                             169,  175,  180,  192,  196,  200,  216,  224,  225,  240,  243,  250,  270,  288,
+                             300,  320,  324,  336,  343,  360,  375,  384,  400,  432,  448,  480,  486,  500,
+                             540,  576,  600,  625,  640,  648,  672,  675,  720,  729,  750,  768,  800,  864,
+                             896,  900,  960,  972,  1000, 1152, 1200, 1250, 1280, 1296, 1440, 1500, 1536, 1600,
+                             1728, 1920, 2000, 2187, 2304, 2400, 2500, 2560, 3000, 3072, 3125, 3200, 3456, 3600,
+                             3840, 4000};
         for(int n : extra)
             s.insert(n);
         return std::vector<int>(s.begin(), s.end());
@@ -279,6 +276,19 @@ int main(int argc, char** argv)
                 // CTAs and column kernels at 64-byte-wide tiles, and the register cap
                 // is set so that as many CTAs as possible stay resident.
                 const bool coop    = strcmp(v.cin, "COOP_NONE") || strcmp(v.cout_, "COOP_NONE");
+                // keep the pool (and the library image) moderate: variants that only matter for
+                // rare layouts are generated for the lengths where they pay
+                const bool pow2 = (n & (n - 1)) == 0;
+                if(v.id == 3 && n > 256)
+                    continue; // planar column tiles: long planar columns use the general row kernel
+                if(v.id == 4 && n > 1024 && !pow2)
+                    continue; // transposing store: second kernel of long 1D transforms
+                if(v.id == 5 && n > 512)
+                    continue; // column-in / row-out
+                if(v.id == 6 && (n % 2 != 0))
+                    continue; // per-rank blocks: multi-device slabs need divisible lengths
+                if((v.id == 15 || v.id == 16) && !pow2)
+                    continue; // experimental full-line persistent kernel
                 const bool realv   = v.id == 7 || v.id == 8; // fused even-length real kernels
                 if(realv && n < 4)
                     continue;

@@ -232,6 +232,7 @@ namespace b200fft
                 constexpr int H     = C::N;
                 constexpr int NP    = H / 2 + 1;
                 constexpr int ITEMS = NP * C::TPB;
+#pragma unroll 4
                 for(int idx = tid; idx < ITEMS; idx += C::THREADS)
                 {
                     const int cc = idx / NP;
@@ -313,25 +314,16 @@ namespace b200fft
                     constexpr int NP    = H / 2 + 1;
                     constexpr int ITEMS = NP * C::TPB;
                     const T       sc    = use_sc ? scale : (T)1;
+                    // p = 0 needs no special case: with Z_H read as Z_0 the general formula gives
+                    // X_0 = Re Z_0 + Im Z_0 and X_H = Re Z_0 - Im Z_0 with zero imaginary parts
+#pragma unroll 4
                     for(int idx = tid; idx < ITEMS; idx += C::THREADS)
                     {
                         const int cc = idx / NP;
                         const int p  = idx % NP;
                         const int q  = H - p;
-                        if(p == 0)
-                        {
-                            const T2 z = sm[C::sidx(cc, 0)];
-                            T2       x0, xh;
-                            x0.x = (z.x + z.y) * sc;
-                            x0.y = 0;
-                            xh.x = (z.x - z.y) * sc;
-                            xh.y = 0;
-                            stage[cc * R::OUT_ROW]     = x0;
-                            stage[cc * R::OUT_ROW + H] = xh;
-                            continue;
-                        }
                         const T2 za = sm[C::sidx(cc, p)];
-                        T2       zb = sm[C::sidx(cc, q)];
+                        T2       zb = sm[C::sidx(cc, p == 0 ? 0 : q)];
                         zb.y        = -zb.y;
                         const T2 w  = htw[p];
                         T2       e, d, tt;
