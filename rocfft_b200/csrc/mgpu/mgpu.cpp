@@ -534,17 +534,46 @@ namespace b200fft
             auto barrier = [&](int slot) {
                 return N.AllReduce(sp->bar + slot, sp->bar + 8 + slot, 1, ncclInt, ncclSum, sp->comm, s) == ncclSuccess;
             };
+            // ROCFFT_B200_MGPU_TIMING=1: print the device time of every phase (synchronises)
+            static const bool timing = getenv("ROCFFT_B200_MGPU_TIMING") != nullptr;
+            cudaEvent_t       ev[6]  = {};
+            auto mark = [&](int i) {
+                if(timing)
+                {
+                    cudaEventCreate(&ev[i]);
+                    cudaEventRecord(ev[i], s);
+                }
+            };
+            mark(0);
             rocfft_status st = execute_core(*sp->passA[0], in, out, nullptr, s);
             if(st != rocfft_status_success)
                 return st;
+            mark(1);
             if(sp->P > 1 && !barrier(0))
                 return rocfft_status_failure;
+            mark(2);
             st = execute_core(*sp->passB[0], in, out, nullptr, s);
             if(st != rocfft_status_success)
                 return st;
+            mark(3);
             if(sp->P > 1 && !barrier(1))
                 return rocfft_status_failure;
-            return execute_core(*sp->passC[0], in, out, nullptr, s);
+            mark(4);
+            st = execute_core(*sp->passC[0], in, out, nullptr, s);
+            mark(5);
+            if(timing)
+            {
+                cudaStreamSynchronize(s);
+                float ms[5];
+                for(int i = 0; i < 5; ++i)
+                    cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
+                fprintf(stderr,
+                        "[rank %d] pass A %.3f ms | barrier %.3f | pass B %.3f | barrier %.3f | pass C %.3f\n",
+                        sp->rank, ms[0], ms[1], ms[2], ms[3], ms[4]);
+                for(auto& e : ev)
+                    cudaEventDestroy(e);
+            }
+            return st;
         }
         if(!info->workBuffer || info->workBufferSize < sp->work_bytes)
             return rocfft_status_invalid_work_buffer; // the NCCL exchange needs a caller-owned work buffer

@@ -154,6 +154,10 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
         l0 = L.b200fft_launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(torch.cuda.current_device()) as cs:
+            # a stream-ordered collective right before the first event lines the GPUs up, so the
+            # timed region does not start with ranks waiting for the slowest host to enqueue
+            align = torch.zeros(1, device="cuda")
+            dist.all_reduce(align)
             e0.record(stream)
             for _ in range(args.steps):
                 step()
@@ -182,6 +186,7 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
             e2e_step()
             torch.cuda.synchronize()
             dist.barrier()
+            dist.all_reduce(align)
             e0.record(stream)
             for _ in range(k):
                 e2e_step()
