@@ -47,14 +47,16 @@ def _digest(paths, extra=""):
     return h.hexdigest()
 
 
-def _deps_text():
-    """Headers every object depends on."""
+def _deps_text(device_only=False):
+    """Headers an object depends on; CUDA sources include nothing from the planner / API / multi-GPU layers."""
     hs = []
     for root, _, files in os.walk(CSRC):
         if os.path.abspath(root).startswith(GEN):
             continue
+        if device_only and os.path.basename(root) in ("api", "mgpu", "gen"):
+            continue
         for f in files:
-            if f.endswith((".h", ".cuh")):
+            if f.endswith((".h", ".cuh")) and not (device_only and f == "planner_impl.h"):
                 hs.append(os.path.join(root, f))
     hs.append(os.path.join(INCLUDE, "rocfft", "rocfft.h"))
     hs.append(os.path.join(INCLUDE, "rocfft_b200_ext.h"))
@@ -96,12 +98,12 @@ def build(small: bool = False, jobs: int | None = None, force: bool = False, ver
         with open(gstamp_file, "w") as f:
             f.write(gstamp)
 
-    deps = _deps_text()
-    dep_hash = _digest(deps)
+    dep_hash_host = _digest(_deps_text())
+    dep_hash_dev = _digest(_deps_text(device_only=True))
     tasks = []
     objs = []
 
-    def add(src, cmd_prefix, flags):
+    def add(src, cmd_prefix, flags, dep_hash):
         name = os.path.relpath(src, CSRC).replace(os.sep, "_")
         obj = os.path.join(OBJ, name + ".o")
         objs.append(obj)
@@ -114,9 +116,9 @@ def build(small: bool = False, jobs: int | None = None, force: bool = False, ver
 
     gen_cu = sorted(os.path.join(GEN, f) for f in os.listdir(GEN) if f.endswith(".cu"))
     for src in gen_cu + [os.path.join(CSRC, s) for s in CUDA_SOURCES]:
-        add(src, [NVCC], NVCC_FLAGS)
+        add(src, [NVCC], NVCC_FLAGS, dep_hash_dev)
     for src in [os.path.join(CSRC, s) for s in HOST_SOURCES] + [os.path.join(GEN, "gen_pool.cpp")]:
-        add(src, ["g++"], CXX_FLAGS)
+        add(src, ["g++"], CXX_FLAGS, dep_hash_host)
 
     t0 = time.time()
     if tasks:

@@ -199,6 +199,7 @@ namespace
         std::vector<int> f;
         size_t           smem;
         std::string      cfg; // the KCfg<...> type
+        bool             push = false; // cluster variants: push-exchange kernel
     };
 
     size_t smem_bytes(int n, int tpb, bool col, int prec, bool coop, int npass)
@@ -300,12 +301,26 @@ int main(int argc, char** argv)
                 if(pairv && (prec != 0 || ch.f.size() < 2 || n < 32))
                     continue;
                 const bool clv   = v.id == 17 || v.id == 18;
-                if(clv && ((n & (n - 1)) != 0 || n < 64 || tpt % 2))
+                // single precision up to 1024 points: the push-exchange cluster kernel with a two-pass
+                // factorisation W0 x W1 (W1 divides W0 <= 32); measured 65 % of the copy rate for
+                // 1024 = 32 x 32 against 51 % for the three-pass pull kernel
+                const bool push = clv && prec == 0 && pow2 && n >= 64 && n <= 1024;
+                int        kt   = tpt; // threads per transform and factors of this kernel
+                std::vector<int> kf = ch.f;
+                if(push)
+                {
+                    int w0 = 8;
+                    while(w0 * w0 < n)
+                        w0 *= 2;
+                    kf = {w0, n / w0};
+                    kt = n / w0;
+                }
+                if(clv && !push && ((n & (n - 1)) != 0 || n < 64 || tpt % 2))
                     continue;
                 const bool widev = v.id == 15 || v.id == 16 || clv;
-                if(widev && (tuned || ch.f.size() < 2 || n < 32 || tpt * 8 > 1024 || ch.f[0] != ept))
+                if(widev && !push && (tuned || ch.f.size() < 2 || n < 32 || tpt * 8 > 1024 || ch.f[0] != ept))
                     continue;
-                if(widev)
+                if(widev && !push)
                 {
                     bool all_divide = true;
                     for(int f : ch.f)
@@ -373,7 +388,12 @@ int main(int argc, char** argv)
                         continue;
                     sm = (size_t)(n + (n >> 4) + 1) * (tpb / 2) * 16;
                 }
-                if(clv)
+                if(push)
+                {
+                    tpb = 128 / esz;
+                    sm  = (size_t)(n / 2) * 128 + 16;
+                }
+                else if(clv)
                 {
                     tpb = 128 / esz;
                     sm  = (size_t)(n / 2 + (n >> 5) + 1) * 128;
@@ -389,8 +409,10 @@ int main(int argc, char** argv)
                 }
                 else if(sm > smem_cap)
                     continue;
-                const int threads = clv ? tpt * 4 : widev ? tpt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
-                int       minb    = std::max(1, 65536 / (threads * ((pairv || clv) ? 128 : regcap)));
+                const int threads = clv ? kt * 4 : widev ? tpt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
+                int       minb    = std::max(1, 65536 / (threads * (push ? 170 : (pairv || clv) ? 128 : regcap)));
+                if(push)
+                    minb = std::min(minb, 4);
                 if(sm)
                     minb = std::min<int>(minb, (int)(200 * 1024 / (sm + 1024)));
                 minb = std::max(1, std::min(minb, 2048 / threads));
@@ -402,19 +424,20 @@ int main(int argc, char** argv)
                 k.n       = n;
                 k.prec    = prec;
                 k.variant = v.id;
-                k.tpt     = tpt;
+                k.tpt     = kt;
                 k.tpb     = tpb;
                 k.minb    = minb;
-                k.f       = ch.f;
+                k.f       = kf;
+                k.push    = push;
                 k.smem    = sm;
                 k.name    = std::string("fft_") + (prec == 0 ? "sp" : "dp") + "_len" + std::to_string(n)
                          + "_" + v.tag;
                 std::string fl = "FactorList<";
-                for(size_t i = 0; i < ch.f.size(); ++i)
-                    fl += (i ? "," : "") + std::to_string(ch.f[i]);
+                for(size_t i = 0; i < kf.size(); ++i)
+                    fl += (i ? "," : "") + std::to_string(kf[i]);
                 fl += ">";
                 k.cfg = std::string("KCfg<") + tname + "," + std::to_string(n) + ","
-                        + std::to_string(tpt) + "," + std::to_string(tpb) + ","
+                        + std::to_string(kt) + "," + std::to_string(tpb) + ","
                         + (v.col ? "true" : "false") + "," + v.ioki + "," + v.ioko + "," + v.cin + "," + v.cout_ + ","
                         + std::to_string(minb) + "," + fl + ">";
                 kernels.push_back(k);
@@ -435,7 +458,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\n#include \"stockham_colcluster.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -453,7 +476,8 @@ int main(int argc, char** argv)
         else if(k.variant == 15 || k.variant == 16)
             o << "launch_colwide_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ">";
         else if(k.variant == 17 || k.variant == 18)
-            o << "launch_colcluster_kernel<" << k.cfg << ", 2, " << (k.variant == 18 ? "true" : "false") << ">";
+            o << (k.push ? "launch_colpush_kernel<" : "launch_colcluster_kernel<") << k.cfg << ", 2, "
+              << (k.variant == 18 ? "true" : "false") << ">";
         else
             o << "launch_tile_kernel<" << k.cfg << ">";
         o << "(*a, ntiles, s);\n}\n\n";

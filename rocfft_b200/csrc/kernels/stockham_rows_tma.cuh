@@ -41,6 +41,10 @@ namespace b200fft
         MODE_C2R = 2,
     };
 
+#ifndef B200FFT_MBAR_SPIN
+#define B200FFT_MBAR_SPIN (1u << 22) // try_wait attempts before a wait gives up
+#endif
+
     namespace ptx
     {
         __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -74,7 +78,7 @@ namespace b200fft
         // bounded wait; false on expiry
         __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity)
         {
-            for(unsigned i = 0; i < (1u << 22); ++i)
+            for(unsigned i = 0; i < B200FFT_MBAR_SPIN; ++i)
                 if(mbar_try_wait(bar, parity))
                     return true;
             return false;

@@ -455,9 +455,13 @@ namespace b200fft
                 // and a cluster-of-two kernel over distributed shared memory (ROCFFT_B200_COLCLUSTER).
                 // Both measured slower than the 64-byte-tile kernels on B200 so far (too few warps
                 // in flight per SM), so they are opt-in.
+                // measured on 2-8 GB arrays: once the row pitch reaches 4 MB every row of a tile lies in
+                // its own page and the 64-byte-tile kernels drop to 45 % of the copy rate whatever the
+                // padding, while the full-line cluster kernel stays at 51 % (half the page touches per byte)
+                const bool huge_pitch = prec_ == 0 && s.n >= 512 && std::llabs(a.in.es) * 8 >= (4ll << 20);
                 if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
                    && (getenv("ROCFFT_B200_COLWIDE") || getenv("ROCFFT_B200_COLCLUSTER")
-                       || (s.out_blk_ptrs && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
+                       || ((s.out_blk_ptrs || huge_pitch) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
                 {
                     // stores that cross NVLink want whole 128-byte lines: the cluster kernel is the
                     // default when the output goes to other ranks' buffers
@@ -483,6 +487,7 @@ namespace b200fft
                         kern                = wk;
                         st.kern             = wk;
                         wide_chosen         = true;
+                        a.aux[3]            = device_error_flag(); // raised if an mbarrier wait gives up
                     }
                 }
                 // single-precision column tiles: two columns per thread when everything is even
@@ -501,7 +506,7 @@ namespace b200fft
                            && (long long)s.n * std::llabs(a.out.es) < (1ll << 31);
                     // measured: with row pitches of megabytes the plain kernel (more threads in
                     // flight per tile) is faster; the paired kernel wins at moderate pitches
-                    even = even && std::llabs(a.in.es) * 8 <= (256ll << 10);
+                    even = even && (std::llabs(a.in.es) * 8 <= (256ll << 10) || getenv("ROCFFT_B200_COLPAIR_ANY_PITCH"));
                     if(even)
                     {
                         st.kern_unaligned   = kern;
