@@ -18,6 +18,15 @@ extern "C" {
  * plan log layer at :3757-3914), returned in a caller buffer instead. */
 ROCFFT_EXPORT rocfft_status b200fft_plan_describe(const rocfft_plan plan, char* buf, size_t len);
 
+/* Kernels that wait on hardware barriers (the bulk-copy row kernels and the
+ * cluster column kernels) bound every wait; when a wait gives up the kernel sets
+ * a flag in plan-owned device memory and carries on so that the launch still
+ * ends.  This call synchronises with the device (a blocking 4-byte copy per
+ * flag) and sets *raised to 1 if any kernel of the plan has ever raised its
+ * flag; results of such an execute are not valid.  No reference counterpart:
+ * the reference's kernels have no such waits. */
+ROCFFT_EXPORT rocfft_status b200fft_plan_device_error(const rocfft_plan plan, int* raised);
+
 /* Host copy of the stacked per-pass twiddle table a Stockham kernel with the
  * given factor list reads (reference layout: library/src/twiddles.cpp:68-106).
  * precision 0 = float pairs, 1 = double pairs.  *needed receives the byte size. */

@@ -300,6 +300,26 @@ class Plan:
     def execute(self, in_ptrs, out_ptrs=None):
         return rocfft_execute(self.plan, in_ptrs, out_ptrs, self.info)
 
+    def describe(self):
+        """Plan text: one line per kernel launch (b200fft_plan_describe)."""
+        L = lib()
+        L.b200fft_plan_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+        buf = ctypes.create_string_buffer(1 << 16)
+        st = L.b200fft_plan_describe(self.plan, buf, len(buf))
+        if st != rocfft_status_success:
+            raise RuntimeError(f"b200fft_plan_describe failed: {st}")
+        return buf.value.decode()
+
+    def device_error(self):
+        """True if a kernel of this plan ever gave up a bounded wait (blocks until the device is idle)."""
+        L = lib()
+        L.b200fft_plan_device_error.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        v = ctypes.c_int(0)
+        st = L.b200fft_plan_device_error(self.plan, ctypes.byref(v))
+        if st != rocfft_status_success:
+            raise RuntimeError(f"b200fft_plan_device_error failed: {st}")
+        return bool(v.value)
+
     def destroy(self):
         if self.info:
             rocfft_execution_info_destroy(self.info)

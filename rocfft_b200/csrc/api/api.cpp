@@ -665,6 +665,26 @@ ROCFFT_EXPORT rocfft_status b200fft_plan_describe(const rocfft_plan plan, char* 
     return rocfft_status_success;
 }
 
+ROCFFT_EXPORT rocfft_status b200fft_plan_device_error(const rocfft_plan plan, int* raised)
+{
+    if(!plan || !raised)
+        return rocfft_status_failure;
+    std::vector<const int*> flags;
+    if(plan->core && plan->core->dev_error)
+        flags.push_back(plan->core->dev_error);
+    if(plan->mgpu)
+        b200fft::multi_device_error_flags(plan, flags);
+    *raised = 0;
+    for(const int* f : flags)
+    {
+        int v = 0;
+        if(cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+            return rocfft_status_failure;
+        *raised |= (v != 0);
+    }
+    return rocfft_status_success;
+}
+
 ROCFFT_EXPORT rocfft_status b200fft_slab_exchange_offsets(int     ranks,
                                                           int     chunks,
                                                           size_t  slab_bytes,

@@ -514,6 +514,17 @@ namespace b200fft
         return o.str();
     }
 
+    void multi_device_error_flags(const rocfft_plan_t* plan, std::vector<const int*>& out)
+    {
+        auto* sp = static_cast<const SlabPlan*>(plan->mgpu);
+        if(!sp)
+            return;
+        for(auto* v : {&sp->passA, &sp->passB, &sp->passC})
+            for(auto& c : *v)
+                if(c && c->dev_error)
+                    out.push_back(c->dev_error);
+    }
+
     rocfft_status execute_multi_device_plan(rocfft_plan_t*                 plan,
                                             void* const*                   in,
                                             void* const*                   out,

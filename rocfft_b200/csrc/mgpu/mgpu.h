@@ -6,6 +6,7 @@
 // global transpose) and library/src/tree_node.cpp:473-928 (communication ops).
 #pragma once
 #include "../plan/plan.h"
+#include <vector>
 
 namespace b200fft
 {
@@ -15,6 +16,8 @@ namespace b200fft
     void          destroy_multi_device_plan(rocfft_plan_t* plan);
     size_t        multi_device_work_bytes(const rocfft_plan_t* plan);
     std::string   describe_multi_device_plan(const rocfft_plan_t* plan);
+    // device error flags (PlanCore::dev_error) of every local pass of the plan; null entries skipped
+    void          multi_device_error_flags(const rocfft_plan_t* plan, std::vector<const int*>& out);
     rocfft_status execute_multi_device_plan(rocfft_plan_t*                 plan,
                                             void* const*                   in,
                                             void* const*                   out,
