@@ -177,9 +177,9 @@ namespace b200fft
             constexpr int NBQ = PN::NB; // row e is consumed by butterfly (e mod NBQ) of pass P+1
             constexpr int PER = NBQ / CL; // butterflies of pass P+1 per CTA
             static_assert(NBQ % CL == 0 && PER % CC::HT == 0, "next pass must split evenly over the cluster");
-            // every CTA of the cluster has taken its inputs of pass P out of its buffer
-            if constexpr(P > 0)
-                ptx::cluster_wait();
+            // P > 0: every CTA of the cluster has taken its inputs of pass P out of its buffer;
+            // P = 0: every CTA has initialised its mbarrier (arrival at the top of the kernel)
+            ptx::cluster_wait();
             if(threadIdx.x == 0)
                 ptx::mbar_expect_tx(bar, CC::PART_BYTES);
             // results of pass P -> the buffers of the CTAs that consume them
@@ -280,9 +280,10 @@ namespace b200fft
             ptx::mbar_init(bar, 1);
             ptx::fence_mbar_init();
         }
-        // every mbarrier of the cluster is initialised before anybody pushes; nothing is
-        // outstanding yet, so the release costs only the barrier's latency
-        ptx::cluster_sync();
+        // every mbarrier of the cluster must be initialised before anybody pushes: the init is
+        // published by fence.mbarrier_init, so a relaxed arrival suffices; the matching wait
+        // stands before the first push, behind the global loads and the butterflies of pass 0
+        ptx::cluster_arrive_relaxed();
 
         const unsigned  tile  = blockIdx.x / CL;
         const TilePos   tp    = decode_tile(a, tile, CC::COLS);

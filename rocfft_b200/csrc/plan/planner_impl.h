@@ -451,17 +451,20 @@ namespace b200fft
                 fill_outer(o, a, st.loops);
                 // column tiles: the persistent full-line kernel when the layout allows it
                 bool wide_chosen = false;
-                // Two full-line designs exist: a persistent one-CTA-per-SM kernel (ROCFFT_B200_COLWIDE)
-                // and a cluster-of-two kernel over distributed shared memory (ROCFFT_B200_COLCLUSTER).
-                // Both measured slower than the 64-byte-tile kernels on B200 so far (too few warps
-                // in flight per SM), so they are opt-in.
-                // measured on 2-8 GB arrays: once the row pitch reaches 4 MB every row of a tile lies in
-                // its own page and the 64-byte-tile kernels drop to 45 % of the copy rate whatever the
-                // padding, while the full-line cluster kernel stays at 51 % (half the page touches per byte)
-                const bool huge_pitch = prec_ == 0 && s.n >= 512 && std::llabs(a.in.es) * 8 >= (4ll << 20);
+                // Two full-line designs exist: a persistent one-CTA-per-SM kernel (ROCFFT_B200_COLWIDE,
+                // experimental) and cluster-of-two kernels over distributed shared memory
+                // (ROCFFT_B200_COLCLUSTER forces them, ROCFFT_B200_NO_COLCLUSTER forbids them).
+                // Measured (fp32): the push-exchange cluster kernel (128-byte-wide tiles) runs a 1024-point
+                // column pass at 67 % of the copy rate whatever the row pitch, the 64-byte-tile kernels at
+                // 57-67 % for pitches up to 2 MB and 45 % from 4 MB on (every row of a tile in its own page).
+                // 512 points: the cluster kernel wins at megabyte pitches (512^3: 1.30 vs 1.50 ms), loses at
+                // small ones (512 x 512 x 512 images: 0.82 vs 0.78 ms); 256 points: it loses.
+                const long long pitch_bytes = std::llabs(a.in.es) * 8;
+                const bool      prefer_cluster
+                    = prec_ == 0 && s.n <= 1024 && (s.n >= 1024 || (s.n >= 512 && pitch_bytes >= (1ll << 20)));
                 if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
                    && (getenv("ROCFFT_B200_COLWIDE") || getenv("ROCFFT_B200_COLCLUSTER")
-                       || ((s.out_blk_ptrs || huge_pitch) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
+                       || ((s.out_blk_ptrs || prefer_cluster) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
                 {
                     // stores that cross NVLink want whole 128-byte lines: the cluster kernel is the
                     // default when the output goes to other ranks' buffers
