@@ -35,8 +35,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", INCLUDE, "-I", os.path.join(CUDA, "include"),
              "-I", os.path.join(CSRC, "launch"), "-I", os.path.join(CSRC, "kernels"), "-Wall"]
 
-HOST_SOURCES = ["api/api.cpp", "plan/planner.cpp", "plan/twiddles.cpp", "plan/execute.cpp", "mgpu/mgpu.cpp"]
-CUDA_SOURCES = ["launch/elementwise.cu", "launch/noalloc.cu"]
+HOST_SOURCES = ["api/api.cpp", "plan/planner.cpp", "plan/twiddles.cpp", "plan/execute.cpp", "mgpu/mgpu.cpp", "mgpu/gather_scatter.cpp"]
+CUDA_SOURCES = ["launch/elementwise.cu", "launch/noalloc.cu", "launch/brick_copy.cu"]
 
 
 def _digest(paths, extra=""):

@@ -435,6 +435,7 @@ rocfft_status rocfft_plan_create(rocfft_plan*                  plan,
                 return rocfft_status_invalid_dimensions;
         p->rank = dimensions;
         p->lengths.assign(lengths, lengths + dimensions);
+        p->userLengths = p->lengths;
         p->batch         = number_of_transforms;
         p->placement     = placement;
         p->precision     = precision;

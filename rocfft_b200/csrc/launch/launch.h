@@ -89,6 +89,16 @@ typedef enum b200fft_ew_kind
 
 cudaError_t b200fft_launch_elementwise(int kind, int precision, const b200fft_eargs* a, cudaStream_t stream);
 
+// strided box copy between a brick and the full field (launch/brick_copy.cu); elem_bytes 4 / 8 / 16,
+// four extents and element strides per side, fastest dimension first
+cudaError_t b200fft_launch_brick_copy(void*                     dst,
+                                      const void*               src,
+                                      int                       elem_bytes,
+                                      const unsigned long long* n,
+                                      const long long*          dst_stride,
+                                      const long long*          src_stride,
+                                      cudaStream_t              stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -108,6 +108,7 @@ namespace b200fft
 
         struct SlabPlan
         {
+            MultiDeviceHeader hdr{0};
             ncclComm_t comm  = nullptr;
             int        P     = 1;
             int        rank  = 0;
@@ -174,6 +175,12 @@ namespace b200fft
         const auto& d = plan->desc;
         if(d.inFields.size() != 1 || d.outFields.size() != 1)
             throw std::runtime_error("exactly one input field and one output field are supported");
+        if(d.comm_type == rocfft_comm_none)
+        {
+            // one process drives every brick: gather, transform on one device, scatter
+            build_gather_scatter_plan(plan);
+            return;
+        }
         const bool c2c = plan->transformType == rocfft_transform_type_complex_forward
                          || plan->transformType == rocfft_transform_type_complex_inverse;
         if(!c2c)
@@ -457,6 +464,8 @@ namespace b200fft
 
     void destroy_multi_device_plan(rocfft_plan_t* plan)
     {
+        if(multi_device_kind(plan) == 1)
+            return destroy_gather_scatter_plan(plan);
         auto* sp = static_cast<SlabPlan*>(plan->mgpu);
         if(!sp)
             return;
@@ -493,12 +502,16 @@ namespace b200fft
 
     size_t multi_device_work_bytes(const rocfft_plan_t* plan)
     {
+        if(multi_device_kind(plan) == 1)
+            return gather_scatter_work_bytes(plan);
         auto* sp = static_cast<const SlabPlan*>(plan->mgpu);
         return sp ? sp->work_bytes : 0;
     }
 
     std::string describe_multi_device_plan(const rocfft_plan_t* plan)
     {
+        if(multi_device_kind(plan) == 1)
+            return describe_gather_scatter_plan(plan);
         auto* sp = static_cast<const SlabPlan*>(plan->mgpu);
         if(!sp)
             return "";
@@ -516,6 +529,8 @@ namespace b200fft
 
     void multi_device_error_flags(const rocfft_plan_t* plan, std::vector<const int*>& out)
     {
+        if(multi_device_kind(plan) == 1)
+            return gather_scatter_error_flags(plan, out);
         auto* sp = static_cast<const SlabPlan*>(plan->mgpu);
         if(!sp)
             return;
@@ -530,6 +545,8 @@ namespace b200fft
                                             void* const*                   out,
                                             const rocfft_execution_info_t* info)
     {
+        if(multi_device_kind(plan) == 1)
+            return execute_gather_scatter_plan(plan, in, out, info);
         auto* sp = static_cast<SlabPlan*>(plan->mgpu);
         if(!sp || (!sp->comm_stream && !sp->p2p))
             return rocfft_status_failure;

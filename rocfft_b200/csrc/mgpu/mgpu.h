@@ -10,6 +10,27 @@
 
 namespace b200fft
 {
+    // plan->mgpu points at one of two plan kinds; both start with this header
+    struct MultiDeviceHeader
+    {
+        int kind; // 0: slab plan over an NCCL communicator (mgpu.cpp), 1: gather / scatter plan (gather_scatter.cpp)
+    };
+    inline int multi_device_kind(const rocfft_plan_t* plan)
+    {
+        return plan->mgpu ? static_cast<const MultiDeviceHeader*>(plan->mgpu)->kind : -1;
+    }
+
+    // gather / scatter plans: any brick layout of a single process (gather_scatter.cpp)
+    void          build_gather_scatter_plan(rocfft_plan_t* plan);
+    void          destroy_gather_scatter_plan(rocfft_plan_t* plan);
+    size_t        gather_scatter_work_bytes(const rocfft_plan_t* plan);
+    std::string   describe_gather_scatter_plan(const rocfft_plan_t* plan);
+    void          gather_scatter_error_flags(const rocfft_plan_t* plan, std::vector<const int*>& out);
+    rocfft_status execute_gather_scatter_plan(rocfft_plan_t*                 plan,
+                                              void* const*                   in,
+                                              void* const*                   out,
+                                              const rocfft_execution_info_t* info);
+
     // builds plan->mgpu from the in/out fields of the description; throws on
     // malformed fields (std::runtime_error) so that creation reports failure
     void          build_multi_device_plan(rocfft_plan_t* plan);

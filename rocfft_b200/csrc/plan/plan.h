@@ -142,6 +142,7 @@ struct rocfft_plan_t
 {
     size_t                    rank = 0;
     std::vector<size_t>       lengths, outputLengths;
+    std::vector<size_t>       userLengths; // as passed to rocfft_plan_create, before dimensions are sorted
     size_t                    batch = 1;
     rocfft_result_placement   placement = rocfft_placement_inplace;
     rocfft_transform_type     transformType = rocfft_transform_type_complex_forward;

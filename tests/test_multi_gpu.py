@@ -40,3 +40,17 @@ def test_two_rank_slab_plan(gpu, lengths, prec, direction, placement):
     if gpu.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _launch(2, lengths, prec, direction, placement, 29632)
+
+
+@pytest.mark.parametrize("split", ["slowest_both", "slow_in_fast_out", "pencils"])
+def test_single_process_bricks_on_two_devices(gpu, split):
+    """One process, bricks alternating between two GPUs: the gather / scatter plan reaches the
+    other device through peer access (reference: multi_device_test.cpp with fft_mp_lib_none)."""
+    if gpu.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import rocfft_b200 as rf
+    from test_fields_gpu import SPLITS, TOL, run_field_case
+    gi, go = SPLITS[split]
+    gpu.cuda.set_device(0)
+    err = run_field_case(rf.rocfft_transform_type_complex_forward, 0, [64, 32, 16], 2, gi, go, devices=[0, 1])
+    assert err < TOL[0], err
