@@ -23,11 +23,12 @@
 
 namespace
 {
-    // ---- logging (ROCFFT_LAYER bitmask: 1 trace, 8 plan; auxiliary.cpp:83-137) ----
+    // ---- logging (ROCFFT_LAYER bitmask: 1 trace, 2 bench, 4 profile, 8 plan; include/logging.h:139-150,
+    // auxiliary.cpp:83-137 in the reference) ----
     struct Log
     {
         int           layer = 0;
-        std::ofstream trace_file, plan_file;
+        std::ofstream trace_file, plan_file, bench_file, profile_file;
         std::mutex    mtx;
         std::ostream& trace()
         {
@@ -36,6 +37,14 @@ namespace
         std::ostream& plan()
         {
             return plan_file.is_open() ? (std::ostream&)plan_file : std::cerr;
+        }
+        std::ostream& bench()
+        {
+            return bench_file.is_open() ? (std::ostream&)bench_file : std::cerr;
+        }
+        std::ostream& profile()
+        {
+            return profile_file.is_open() ? (std::ostream&)profile_file : std::cerr;
         }
         void init()
         {
@@ -48,6 +57,12 @@ namespace
             if(const char* p = getenv("ROCFFT_LOG_PLAN_PATH"))
                 if(!plan_file.is_open())
                     plan_file.open(p, std::ios::app);
+            if(const char* p = getenv("ROCFFT_LOG_BENCH_PATH"))
+                if(!bench_file.is_open())
+                    bench_file.open(p, std::ios::app);
+            if(const char* p = getenv("ROCFFT_LOG_PROFILE_PATH"))
+                if(!profile_file.is_open())
+                    profile_file.open(p, std::ios::app);
         }
     };
     Log& log()
@@ -67,6 +82,48 @@ namespace
         s << fn;
         ((s << "," << a), ...);
         l.trace() << s.str() << std::endl;
+    }
+
+    // the rocfft-bench command line that reproduces a plan (bench log layer; the reference builds
+    // the same line in plan.cpp:698-726): row-major lengths and strides, enumerators as integers
+    std::string bench_command(const rocfft_plan_t& p)
+    {
+        std::ostringstream b;
+        b << "rocfft-bench --length ";
+        for(auto it = p.userLengths.rbegin(); it != p.userLengths.rend(); ++it)
+            b << *it << " ";
+        b << "-b " << p.batch << " ";
+        if(p.placement == rocfft_placement_notinplace)
+            b << "-o ";
+        b << "-t " << (int)p.transformType << " --precision "
+          << (p.precision == rocfft_precision_single ? "single" : p.precision == rocfft_precision_double ? "double" : "half")
+          << " --itype " << (int)p.desc.inArrayType << " --otype " << (int)p.desc.outArrayType << " --istride ";
+        for(auto it = p.desc.inStrides.rbegin(); it != p.desc.inStrides.rend(); ++it)
+            b << *it << " ";
+        b << "--ostride ";
+        for(auto it = p.desc.outStrides.rbegin(); it != p.desc.outStrides.rend(); ++it)
+            b << *it << " ";
+        b << "--idist " << p.desc.inDist << " --odist " << p.desc.outDist << " --ioffset ";
+        for(size_t v : p.desc.inOffset)
+            b << v << " ";
+        b << "--ooffset ";
+        for(size_t v : p.desc.outOffset)
+            b << v << " ";
+        return b.str();
+    }
+
+    // peak memory bandwidth for the profile layer: ROCFFT_DEVICE_BW (GB/s) or memory clock x bus width
+    // (powX.cpp:218-255 in the reference)
+    double max_memory_bandwidth_gbs()
+    {
+        if(const char* e = getenv("ROCFFT_DEVICE_BW"))
+            return atof(e);
+        int dev = 0, khz = 0, bits = 0;
+        if(cudaGetDevice(&dev) != cudaSuccess
+           || cudaDeviceGetAttribute(&khz, cudaDevAttrMemoryClockRate, dev) != cudaSuccess
+           || cudaDeviceGetAttribute(&bits, cudaDevAttrGlobalMemoryBusWidth, dev) != cudaSuccess)
+            return 0.0;
+        return 2.0 * khz * 1e3 * (bits / 8.0) / 1e9;
     }
 
     size_t offset_count(rocfft_array_type t)
@@ -453,6 +510,11 @@ rocfft_status rocfft_plan_create(rocfft_plan*                  plan,
            || (!p->desc.outStrides.empty() && p->desc.outStrides.size() != dimensions))
             return rocfft_status_invalid_strides;
         init_defaults(p->desc, transform_type, placement, p->lengths, p->outputLengths);
+        if(log().layer & 2)
+        {
+            std::lock_guard<std::mutex> g(log().mtx);
+            log().bench() << bench_command(*p) << std::endl;
+        }
         sort_dims(*p);
         rocfft_status st = check_array_types(*p);
         if(st != rocfft_status_success)
@@ -636,6 +698,41 @@ rocfft_status rocfft_execute(const rocfft_plan     plan,
                     return rocfft_status_failure;
                 own_alloc = true;
             }
+        }
+        if(log().layer & 4)
+        {
+            // profile layer: time every kernel with events, wait, report (this synchronises the stream)
+            const size_t             n = core.steps.size();
+            std::vector<cudaEvent_t> ev(n + 1);
+            for(auto& e : ev)
+                cudaEventCreate(&e);
+            rocfft_status st = b200fft::execute_core(core, in_buffer, out_buffer, work, ei.stream, ev.data());
+            if(own_alloc)
+                cudaFreeAsync(work, ei.stream);
+            cudaStreamSynchronize(ei.stream);
+            const double peak = max_memory_bandwidth_gbs();
+            for(size_t i = 0; i < n; ++i)
+            {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+                const b200fft::Step& sp    = core.steps[i];
+                unsigned long long   elems = 0;
+                if(sp.kind == b200fft::Step::TILE && sp.kern)
+                {
+                    elems = (unsigned long long)sp.kern->length * sp.ka.on[0] * sp.ka.on[1] * sp.ka.on[2];
+                    for(const auto& l : sp.loops)
+                        elems *= l.count;
+                }
+                const unsigned long long bytes = elems * (sp.in_elem_bytes + sp.out_elem_bytes);
+                const double             gbs   = ms > 0 ? bytes / (ms * 1e6) : 0.0;
+                std::lock_guard<std::mutex> g(log().mtx);
+                log().profile() << "rocfft_execute,scheme," << sp.note << ",duration_ms," << ms << ",total_size_bytes,"
+                                << bytes << ",exec_GB_s," << gbs << ",max_mem_GB_s," << peak << ",bw_efficiency_pct,"
+                                << (peak > 0 ? 100.0 * gbs / peak : 0.0) << ",kernel_index," << i << std::endl;
+            }
+            for(auto& e : ev)
+                cudaEventDestroy(e);
+            return st;
         }
         rocfft_status st = b200fft::execute_core(core, in_buffer, out_buffer, work, ei.stream);
         if(own_alloc)

@@ -188,3 +188,24 @@ def test_stacked_twiddle_table_matches_pass_model(L):
             cur = nxt
         ref = orc.c2c(x[None, :], -1)[0]
         assert np.max(np.abs(cur - ref)) < 1e-11 * np.max(np.abs(ref)), (n, factors)
+
+
+def test_log_layers_write_trace_bench_and_plan_files(tmp_path):
+    """ROCFFT_LAYER bits 1 (trace), 2 (bench: an equivalent rocfft-bench command line) and 8 (plan)
+    write to the files named by ROCFFT_LOG_*_PATH (reference: library/src/auxiliary.cpp:83-137,
+    library/src/plan.cpp:698-726)."""
+    import subprocess
+    import sys
+    env = dict(os.environ, ROCFFT_LAYER="11", ROCFFT_LOG_TRACE_PATH=str(tmp_path / "trace.log"),
+               ROCFFT_LOG_BENCH_PATH=str(tmp_path / "bench.log"), ROCFFT_LOG_PLAN_PATH=str(tmp_path / "plan.log"))
+    code = ("import rocfft_b200 as rf; rf.rocfft_setup();"
+            "p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_real_forward, 0, [1000, 30], 16);"
+            "p.destroy(); rf.rocfft_cleanup()")
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    bench = (tmp_path / "bench.log").read_text().strip()
+    assert bench == ("rocfft-bench --length 30 1000 -b 16 -o -t 2 --precision single --itype 2 --otype 3 "
+                     "--istride 1000 1 --ostride 501 1 --idist 30000 --odist 15030 --ioffset 0 0 --ooffset 0 0")
+    trace = (tmp_path / "trace.log").read_text()
+    assert "rocfft_plan_create" in trace and "rocfft_plan_destroy" in trace
+    assert "len500_row_r2c" in (tmp_path / "plan.log").read_text()
