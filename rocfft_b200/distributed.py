@@ -159,8 +159,10 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
             align = torch.zeros(1, device="cuda")
             dist.all_reduce(align)
             e0.record(stream)
+            h0 = time.perf_counter()
             for _ in range(args.steps):
                 step()
+            host_ms = (time.perf_counter() - h0) * 1e3 / args.steps  # host time to enqueue one step
             e1.record(stream)
             torch.cuda.synchronize()
         dist.barrier()
@@ -244,7 +246,7 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
                              "frac": a2a_bytes / ms_max / 1e6 / 770.0, "traffic": None,
                              "note": "bytes each GPU must send over NVLink per transform / step time",
                              "local_hbm_bytes_per_gpu": per_gpu_bytes},
-                "clocks": cs.summary(), "gpu_launches": launches}
+                "clocks": cs.summary(), "gpu_launches": launches, "host_enqueue_ms_per_step": host_ms}
         if e2e:
             line["e2e"] = e2e
         print(json.dumps(line), flush=True)
