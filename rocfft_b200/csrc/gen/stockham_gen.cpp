@@ -445,6 +445,82 @@ int main(int argc, char** argv)
         }
     }
 
+    // ---- small 2D transforms in one kernel (stockham_2d.cuh) ----
+    // Both dimensions come from one family with a common number of points per thread, so that
+    // the row phase and the column phase use the same threads: powers of two with 8 points per
+    // thread, powers of three with 9.  The whole image and the column exchange tile must fit
+    // shared memory and 1024 threads.
+    struct Kernel2D
+    {
+        std::string      name, cfg0, cfg1;
+        int              n0, n1, prec, threads, minb;
+        std::vector<int> f0, f1;
+        size_t           smem;
+    };
+    std::vector<Kernel2D> kernels2d;
+    if(!g_small)
+    {
+        auto fam_factors = [](int n, int ept) {
+            std::vector<int> f;
+            int              r = n;
+            while(r % ept == 0 && r > 1)
+            {
+                f.push_back(ept);
+                r /= ept;
+            }
+            if(r > 1)
+                f.push_back(r);
+            return f;
+        };
+        struct Family
+        {
+            int              ept;
+            std::vector<int> lens;
+        };
+        const Family fams[] = {{8, {8, 16, 32, 64, 128}}, {9, {9, 27, 81}}};
+        for(int prec = 0; prec < 2; ++prec)
+            for(const Family& fam : fams)
+                for(int n0 : fam.lens)
+                    for(int n1 : fam.lens)
+                    {
+                        const int esz  = prec == 0 ? 8 : 16;
+                        const int ps   = prec == 0 ? 4 : 3;
+                        const auto f0 = fam_factors(n0, fam.ept), f1 = fam_factors(n1, fam.ept);
+                        const int threads = n0 * n1 / fam.ept;
+                        if(threads > 1024 || threads < 32)
+                            continue;
+                        const size_t npad0 = (size_t)((n0 + (n0 >> ps)) | 1);
+                        const size_t smem  = (size_t)esz * (npad0 * n1 + (f1.size() > 1 ? (size_t)n1 * n0 : 0));
+                        if(smem > 160 * 1024)
+                            continue;
+                        Kernel2D k;
+                        k.n0 = n0;
+                        k.n1 = n1;
+                        k.prec = prec;
+                        k.threads = threads;
+                        k.f0 = f0;
+                        k.f1 = f1;
+                        k.smem = smem;
+                        k.minb = std::max(1, std::min({2048 / threads, (int)(200 * 1024 / (smem + 1024)), 8}));
+                        const char* tname = prec == 0 ? "float" : "double";
+                        auto fl = [](const std::vector<int>& f) {
+                            std::string s = "FactorList<";
+                            for(size_t i = 0; i < f.size(); ++i)
+                                s += (i ? "," : "") + std::to_string(f[i]);
+                            return s + ">";
+                        };
+                        k.cfg0 = std::string("KCfg<") + tname + "," + std::to_string(n0) + "," + std::to_string(n0 / fam.ept)
+                                 + "," + std::to_string(n1) + ",false,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE,"
+                                 + std::to_string(k.minb) + "," + fl(f0) + ">";
+                        k.cfg1 = std::string("KCfg<") + tname + "," + std::to_string(n1) + "," + std::to_string(n1 / fam.ept)
+                                 + "," + std::to_string(n0) + ",true,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE,"
+                                 + std::to_string(k.minb) + "," + fl(f1) + ">";
+                        k.name = std::string("fft2d_") + (prec == 0 ? "sp" : "dp") + "_" + std::to_string(n0) + "x"
+                                 + std::to_string(n1);
+                        kernels2d.push_back(k);
+                    }
+    }
+
     // ---- kernel sources, spread over nfiles translation units ----
     // order by length descending so that expensive kernels spread evenly
     std::vector<size_t> order(kernels.size());
@@ -458,7 +534,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -481,6 +557,15 @@ int main(int argc, char** argv)
         else
             o << "launch_tile_kernel<" << k.cfg << ">";
         o << "(*a, ntiles, s);\n}\n\n";
+    }
+
+    for(size_t i = 0; i < kernels2d.size(); ++i)
+    {
+        const Kernel2D& k = kernels2d[i];
+        auto&           o = files[i % nfiles];
+        o << "extern \"C\" cudaError_t b200fft_launch_" << k.name
+          << "(const b200fft_kargs* a, unsigned long long nimages, cudaStream_t s)\n{\n    return launch_2d_kernel<"
+          << k.cfg0 << ", " << k.cfg1 << ", " << k.minb << ">(*a, nimages, s);\n}\n\n";
     }
 
     // ---- function pool ----
@@ -506,8 +591,28 @@ int main(int argc, char** argv)
             o << "}, " << k.smem << "ull, b200fft_launch_" << k.name << ", \"" << k.name << "\"},\n";
         }
         o << "};\n\nextern \"C\" const b200fft_pool_entry* b200fft_pool(size_t* count)\n{\n"
-             "    *count = sizeof(kPool) / sizeof(kPool[0]);\n    return kPool;\n}\n";
+             "    *count = sizeof(kPool) / sizeof(kPool[0]);\n    return kPool;\n}\n\n";
+        for(const Kernel2D& k : kernels2d)
+            o << "extern \"C\" cudaError_t b200fft_launch_" << k.name
+              << "(const b200fft_kargs*, unsigned long long, cudaStream_t);\n";
+        o << "\nstatic const b200fft_pool2d_entry kPool2D[] = {\n";
+        for(const Kernel2D& k : kernels2d)
+        {
+            o << "    {{" << k.n0 * k.n1 << ", " << k.prec << ", 19, " << k.n0 / (k.f0[0]) << ", " << k.n1 << ", " << k.threads
+              << ", " << k.f0.size() << ", {";
+            for(size_t i = 0; i < 8; ++i)
+                o << (i ? "," : "") << (i < k.f0.size() ? k.f0[i] : 0);
+            o << "}, " << k.smem << "ull, b200fft_launch_" << k.name << ", \"" << k.name << "\"}, " << k.n0 << ", " << k.n1
+              << ", " << k.f1.size() << ", {";
+            for(size_t i = 0; i < 8; ++i)
+                o << (i ? "," : "") << (i < k.f1.size() ? k.f1[i] : 0);
+            o << "}},\n";
+        }
+        if(kernels2d.empty())
+            o << "    {{0, 0, 19, 0, 0, 0, 0, {0,0,0,0,0,0,0,0}, 0ull, nullptr, \"\"}, 0, 0, 0, {0,0,0,0,0,0,0,0}},\n";
+        o << "};\n\nextern \"C\" const b200fft_pool2d_entry* b200fft_pool2d(size_t* count)\n{\n    *count = "
+          << kernels2d.size() << ";\n    return kPool2D;\n}\n";
     }
-    fprintf(stderr, "stockham_gen: %zu kernels in %d files\n", kernels.size(), nfiles);
+    fprintf(stderr, "stockham_gen: %zu kernels (+ %zu fused 2D) in %d files\n", kernels.size(), kernels2d.size(), nfiles);
     return 0;
 }

@@ -69,6 +69,19 @@ typedef struct b200fft_pool_entry
 // generated table of every compiled Stockham kernel
 const b200fft_pool_entry* b200fft_pool(size_t* count);
 
+// whole small 2D transforms in one kernel (kernels/stockham_2d.cuh).  `base` describes the row
+// phase (length = n0 * n1 points per image, factors of n0); the launcher's tile count is the
+// number of images.
+#define B200FFT_2D_SINGLE 19
+typedef struct b200fft_pool2d_entry
+{
+    b200fft_pool_entry base;
+    int                n0, n1; // n0 = fastest dimension
+    int                nfactors1;
+    int                factors1[8]; // factors of n1
+} b200fft_pool2d_entry;
+const b200fft_pool2d_entry* b200fft_pool2d(size_t* count);
+
 // ---- element-wise helper kernels (elementwise.cu) -------------------------
 // Every launcher enqueues on `stream` and returns the launch status.
 typedef enum b200fft_ew_kind

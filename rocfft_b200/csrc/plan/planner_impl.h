@@ -44,18 +44,28 @@ namespace b200fft
 
         inline const b200fft_pool_entry* pool_find(size_t n, int prec, int variant)
         {
-            static std::map<std::tuple<size_t, int, int>, const b200fft_pool_entry*> index;
-            static bool                                                            built = false;
-            if(!built)
-            {
+            // built once, by whichever thread gets here first (plans may be created concurrently)
+            static const std::map<std::tuple<size_t, int, int>, const b200fft_pool_entry*> index = [] {
+                std::map<std::tuple<size_t, int, int>, const b200fft_pool_entry*> m;
                 size_t                    cnt = 0;
                 const b200fft_pool_entry* p   = b200fft_pool(&cnt);
                 for(size_t i = 0; i < cnt; ++i)
-                    index[{(size_t)p[i].length, p[i].precision, p[i].variant}] = &p[i];
-                built = true;
-            }
+                    m[{(size_t)p[i].length, p[i].precision, p[i].variant}] = &p[i];
+                return m;
+            }();
             auto it = index.find({n, prec, variant});
             return it == index.end() ? nullptr : it->second;
+        }
+
+        // whole n0 x n1 transform in one kernel (n0 = fastest dimension), if the pool has it
+        inline const b200fft_pool2d_entry* pool2d_find(size_t n0, size_t n1, int prec)
+        {
+            size_t                      cnt = 0;
+            const b200fft_pool2d_entry* p   = b200fft_pool2d(&cnt);
+            for(size_t i = 0; i < cnt; ++i)
+                if((size_t)p[i].n0 == n0 && (size_t)p[i].n1 == n1 && p[i].base.precision == prec)
+                    return &p[i];
+            return nullptr;
         }
 
         inline bool pool_has(size_t n, int prec)
@@ -138,12 +148,16 @@ namespace b200fft
             }
             const void* stacked_twiddles(const b200fft_pool_entry* k)
             {
-                auto key = std::make_pair(k->length, std::vector<int>(k->factors, k->factors + k->nfactors));
+                return stacked_twiddles(k->length, k->factors, k->nfactors);
+            }
+            const void* stacked_twiddles(int length, const int* factors, int nfactors)
+            {
+                auto key = std::make_pair(length, std::vector<int>(factors, factors + nfactors));
                 auto it  = tw_cache_.find(key);
                 if(it != tw_cache_.end())
                     return it->second;
                 std::vector<char> h;
-                host_stacked_twiddles(k->length, k->factors, k->nfactors, prec_, h);
+                host_stacked_twiddles(length, factors, nfactors, prec_, h);
                 const void* d  = upload(h);
                 tw_cache_[key] = d;
                 return d;
@@ -809,7 +823,48 @@ namespace b200fft
                     emit_copy(c);
                     return;
                 }
-                for(size_t d = 0; d < rank; ++d)
+                size_t first = 0;
+                // the two fastest dimensions in one kernel when the pool has the pair: one pass instead of two
+                if(rank >= 2 && !getenv("ROCFFT_B200_NO_2D_SINGLE"))
+                    if(const b200fft_pool2d_entry* k2 = pool2d_find(in.len[0], in.len[1], prec_))
+                    {
+                        std::vector<OuterDim> o;
+                        for(size_t k = 2; k < rank; ++k)
+                            o.push_back({out.len[k], in.stride[k], out.stride[k]});
+                        o.push_back({in.batch, in.dist, out.dist});
+                        drop_unit_dims(o);
+                        bool empty = false;
+                        for(const auto& d : o)
+                            empty = empty || d.len == 0;
+                        if(empty)
+                            return;
+                        Step st;
+                        st.kind          = Step::TILE;
+                        st.kern          = &k2->base;
+                        st.in            = in.buf;
+                        st.out           = out.buf;
+                        b200fft_kargs& a = st.ka;
+                        a.in.es          = in.stride[0];
+                        a.in.bs          = in.stride[1];
+                        a.out.es         = out.stride[0];
+                        a.out.bs         = out.stride[1];
+                        a.in.planar      = in.buf.planar;
+                        a.out.planar     = out.buf.planar;
+                        fill_outer(o, a, st.loops);
+                        a.ntile0    = a.on[0];
+                        a.inverse   = inverse;
+                        a.use_scale = rank == 2 && use_scale;
+                        a.scale     = scale;
+                        a.twiddles  = stacked_twiddles(k2->n0, k2->base.factors, k2->base.nfactors);
+                        a.aux[1]    = stacked_twiddles(k2->n1, k2->factors1, k2->nfactors1);
+                        st.ntiles   = (unsigned long long)a.on[0] * a.on[1] * a.on[2];
+                        st.in_elem_bytes  = elem_bytes(in.buf);
+                        st.out_elem_bytes = elem_bytes(out.buf);
+                        st.note           = k2->base.name;
+                        core_.steps.push_back(st);
+                        first = 2;
+                    }
+                for(size_t d = first; d < rank; ++d)
                 {
                     const DataView& src = (d == 0) ? in : out;
                     Stage           s;

@@ -102,6 +102,32 @@ def test_c2c_nd(gpu, case):
     _run(case)
 
 
+def cases_2d_single():
+    """Pairs of lengths that the pool holds as one fused 2D kernel (reference scheme CS_KERNEL_2D_SINGLE),
+    in every layout flavour; pairs outside the pool fall back to two passes and must agree as well."""
+    out = []
+    for prec in ("single", "double"):
+        for lens in ([16, 16], [32, 8], [8, 128], [64, 64], [128, 64], [64, 128], [32, 128], [27, 9], [9, 81], [81, 81],
+                     [27, 81]):
+            out.append(Case(C2C_FWD, prec, lens, 5, OOP))
+            out.append(Case(C2C_INV, prec, lens, 3, IP))
+        out.append(Case(C2C_FWD, prec, [64, 32], 3, OOP, CP, CP))
+        out.append(Case(C2C_INV, prec, [32, 64], 3, OOP, CI, CP))
+        out.append(Case(C2C_FWD, prec, [16, 64], 2, IP, CP, CP))
+        out.append(Case(C2C_FWD, prec, [64, 16], 3, OOP, CI, CI, [1, 70], [2, 130], 70 * 16 + 3, 130 * 16 + 7))
+        out.append(Case(C2C_FWD, prec, [32, 32], 2, OOP, CI, CI, [32, 1], [32, 1], 1024, 1024))  # slowest-first
+        out.append(Case(C2C_FWD, prec, [64, 64], 4, OOP, scale=1.0 / 64))
+        out.append(Case(C2C_INV, prec, [64, 64, 6], 2, IP, scale=0.5))
+        out.append(Case(C2C_FWD, prec, [32, 16, 100], 1, OOP))
+        out.append(Case(C2C_FWD, prec, [27, 27, 27], 2, IP))
+    return out
+
+
+@pytest.mark.parametrize("case", cases_2d_single(), ids=lambda c: c.ident())
+def test_c2c_2d_single_kernel(gpu, case):
+    _run(case)
+
+
 def cases_real():
     out = []
     for prec in ("single", "double"):

@@ -209,3 +209,19 @@ def test_log_layers_write_trace_bench_and_plan_files(tmp_path):
     trace = (tmp_path / "trace.log").read_text()
     assert "rocfft_plan_create" in trace and "rocfft_plan_destroy" in trace
     assert "len500_row_r2c" in (tmp_path / "plan.log").read_text()
+
+
+def test_small_2d_transforms_use_one_fused_kernel(L):
+    """64 x 64 (and 64 x 64 x n: the two fastest dimensions) plan as one fused 2D kernel; a pair outside
+    the pool plans as two passes."""
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [64, 64], 10)
+    text = p.describe()
+    assert "fft2d_sp_64x64" in text and text.count("  [") == 1, text
+    p.destroy()
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [27, 81, 5], 2)
+    text = p.describe()
+    assert "fft2d_dp_27x81" in text and text.count("  [") == 2, text
+    p.destroy()
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [64, 100], 10)
+    assert "fft2d" not in p.describe()
+    p.destroy()
