@@ -40,31 +40,7 @@
 
 namespace b200fft
 {
-    namespace
-    {
-        // NCCL is resolved at run time so that the library loads (and everything
-        // single-GPU works) on machines without it.
-        struct NcclApi
-        {
-            void* handle = nullptr;
-            ncclResult_t (*GetUniqueId)(ncclUniqueId*)                                          = nullptr;
-            ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int)                    = nullptr;
-            ncclResult_t (*CommDestroy)(ncclComm_t)                                              = nullptr;
-            ncclResult_t (*CommCount)(const ncclComm_t, int*)                                    = nullptr;
-            ncclResult_t (*CommUserRank)(const ncclComm_t, int*)                                 = nullptr;
-            ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
-            ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t)   = nullptr;
-            ncclResult_t (*GroupStart)()                                                         = nullptr;
-            ncclResult_t (*GroupEnd)()                                                           = nullptr;
-            ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t)
-                = nullptr;
-            ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t)
-                = nullptr;
-            const char* (*GetErrorString)(ncclResult_t) = nullptr;
-            bool ok                                     = false;
-        };
-
-        NcclApi& nccl()
+    NcclApi& nccl()
         {
             static NcclApi        api;
             static std::once_flag once;
@@ -96,6 +72,8 @@ namespace b200fft
             return api;
         }
 
+    namespace
+    {
         void nccl_check(ncclResult_t r, const char* what)
         {
             if(r != ncclSuccess)
@@ -181,19 +159,10 @@ namespace b200fft
             build_gather_scatter_plan(plan);
             return;
         }
-        const bool c2c = plan->transformType == rocfft_transform_type_complex_forward
-                         || plan->transformType == rocfft_transform_type_complex_inverse;
-        if(!c2c)
-            throw std::runtime_error("multi-device plans support complex transforms only");
-        if(d.inArrayType != rocfft_array_type_complex_interleaved
-           || d.outArrayType != rocfft_array_type_complex_interleaved)
-            throw std::runtime_error("multi-device plans need interleaved complex data");
+        if(d.comm_type != rocfft_comm_nccl || !d.comm_handle)
+            throw std::runtime_error("multi-process plans need an NCCL communicator (rocfft_comm_nccl)");
         if(plan->precision == rocfft_precision_half)
             throw std::runtime_error("half precision is not supported");
-        if(d.comm_type != rocfft_comm_nccl || !d.comm_handle)
-            throw std::runtime_error("multi-device plans need an NCCL communicator (rocfft_comm_nccl)");
-        if(plan->rank != 3 || plan->batch != 1)
-            throw std::runtime_error("multi-device plans support rank-3, batch-1 transforms");
         NcclApi& N = nccl();
         if(!N.ok)
             throw std::runtime_error("libnccl could not be loaded");
@@ -204,53 +173,68 @@ namespace b200fft
         nccl_check(N.CommUserRank(sp->comm, &sp->rank), "ncclCommUserRank");
         cudaGetDevice(&sp->device);
         sp->csize = plan->precision == rocfft_precision_single ? 8 : 16;
-        sp->nx    = plan->lengths[0];
-        sp->ny    = plan->lengths[1];
-        sp->nz    = plan->lengths[2];
         const int P = sp->P;
-        if(sp->nz % P || sp->ny % P)
-            throw std::runtime_error("slab decomposition needs lengths divisible by the number of ranks");
-        sp->lz = sp->nz / P;
-        sp->ly = sp->ny / P;
 
-        // every rank contributes exactly its own brick; check it is the Z-slab of
-        // this rank with contiguous strides, on both sides
-        auto check_field = [&](const rocfft_field_t& f) {
-            if(f.bricks.size() != 1)
-                throw std::runtime_error("each rank must add exactly one brick per field");
-            const rocfft_brick_t& b = f.bricks[0];
-            if(b.lower.size() != 4)
-                throw std::runtime_error("bricks of a rank-3 transform have 4 coordinates (batch last)");
-            const size_t lo[4] = {0, 0, sp->rank * sp->lz, 0};
-            const size_t hi[4] = {sp->nx, sp->ny, (sp->rank + 1) * sp->lz, 1};
-            const size_t st[4] = {1, sp->nx, sp->nx * sp->ny, sp->nx * sp->ny * sp->lz};
-            for(int i = 0; i < 4; ++i)
-                if(b.lower[i] != lo[i] || b.upper[i] != hi[i] || (i < 3 && b.stride[i] != st[i]))
-                    throw std::runtime_error("bricks must be contiguous slabs of the slowest dimension, one per rank in rank order");
-        };
-        check_field(d.inFields[0]);
-        check_field(d.outFields[0]);
-
-        // agree on the brick layout across ranks: all-gather (lower_z, upper_z) and verify
+        // The optimised plan takes rank-3, batch-1 complex transforms whose fields are one contiguous
+        // Z-slab per rank, in rank order, with lengths divisible by the number of ranks.  Everything
+        // else goes through the gather / scatter plan; all ranks must take the same branch, so they
+        // agree on it first.
+        const bool c2c = plan->transformType == rocfft_transform_type_complex_forward
+                         || plan->transformType == rocfft_transform_type_complex_inverse;
+        bool slab_ok = c2c && d.inArrayType == rocfft_array_type_complex_interleaved
+                       && d.outArrayType == rocfft_array_type_complex_interleaved && plan->rank == 3 && plan->batch == 1
+                       && plan->lengths == plan->userLengths;
+        if(slab_ok)
         {
-            unsigned long long mine[2] = {(unsigned long long)d.inFields[0].bricks[0].lower[2],
-                                          (unsigned long long)d.inFields[0].bricks[0].upper[2]};
-            unsigned long long* dbuf   = nullptr;
-            if(cudaMalloc(&dbuf, sizeof(mine) * (P + 1)) != cudaSuccess)
+            sp->nx  = plan->lengths[0];
+            sp->ny  = plan->lengths[1];
+            sp->nz  = plan->lengths[2];
+            slab_ok = sp->nz % P == 0 && sp->ny % P == 0;
+        }
+        if(slab_ok)
+        {
+            sp->lz = sp->nz / P;
+            sp->ly = sp->ny / P;
+            auto is_slab = [&](const rocfft_field_t& f) {
+                if(f.bricks.size() != 1)
+                    return false;
+                const rocfft_brick_t& b = f.bricks[0];
+                if(b.lower.size() != 4 || b.upper.size() != 4 || b.stride.size() != 4)
+                    return false;
+                const size_t lo[4] = {0, 0, sp->rank * sp->lz, 0};
+                const size_t hi[4] = {sp->nx, sp->ny, (sp->rank + 1) * sp->lz, 1};
+                const size_t st[4] = {1, sp->nx, sp->nx * sp->ny, sp->nx * sp->ny * sp->lz};
+                for(int i = 0; i < 4; ++i)
+                    if(b.lower[i] != lo[i] || b.upper[i] != hi[i] || (i < 3 && b.stride[i] != st[i]))
+                        return false;
+                return true;
+            };
+            slab_ok = is_slab(d.inFields[0]) && is_slab(d.outFields[0]);
+        }
+        {
+            int  mine = slab_ok ? 1 : 0;
+            int* dbuf = nullptr;
+            if(cudaMalloc(&dbuf, sizeof(int) * (P + 1)) != cudaSuccess)
                 throw std::runtime_error("cudaMalloc failed");
-            cudaMemcpy(dbuf, mine, sizeof mine, cudaMemcpyHostToDevice);
-            ncclResult_t r = N.AllGather(dbuf, dbuf + 2, sizeof mine, ncclChar, sp->comm, nullptr);
-            cudaError_t  e = cudaStreamSynchronize(nullptr);
-            std::vector<unsigned long long> all(2 * P);
-            cudaMemcpy(all.data(), dbuf + 2, sizeof(mine) * P, cudaMemcpyDeviceToHost);
+            cudaMemcpy(dbuf, &mine, sizeof mine, cudaMemcpyHostToDevice);
+            ncclResult_t     r = N.AllGather(dbuf, dbuf + 1, sizeof mine, ncclChar, sp->comm, nullptr);
+            cudaError_t      e = cudaStreamSynchronize(nullptr);
+            std::vector<int> all(P);
+            cudaMemcpy(all.data(), dbuf + 1, sizeof(int) * P, cudaMemcpyDeviceToHost);
             cudaFree(dbuf);
             nccl_check(r, "ncclAllGather");
             if(e != cudaSuccess)
                 throw std::runtime_error("brick exchange failed");
-            for(int q = 0; q < P; ++q)
-                if(all[2 * q] != q * sp->lz || all[2 * q + 1] != (q + 1) * sp->lz)
-                    throw std::runtime_error("ranks disagree on the slab layout");
+            for(int v : all)
+                slab_ok = slab_ok && v;
         }
+        if(!slab_ok && !getenv("ROCFFT_B200_MGPU_NO_GATHER"))
+        {
+            build_gather_scatter_plan(plan);
+            return;
+        }
+        if(!slab_ok)
+            throw std::runtime_error("brick layout is not one Z-slab per rank");
 
         // Exchange mode.  Default: peer-to-peer stores from inside the FFT kernels.
         // ROCFFT_B200_MGPU_NCCL=1 selects the NCCL send/recv exchange instead.

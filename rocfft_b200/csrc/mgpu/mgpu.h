@@ -6,10 +6,35 @@
 // global transpose) and library/src/tree_node.cpp:473-928 (communication ops).
 #pragma once
 #include "../plan/plan.h"
+#include <nccl.h>
 #include <vector>
 
 namespace b200fft
 {
+    // NCCL is resolved at run time so that the library loads (and everything
+    // single-GPU works) on machines without it.
+    struct NcclApi
+    {
+        void* handle = nullptr;
+        ncclResult_t (*GetUniqueId)(ncclUniqueId*)                                          = nullptr;
+        ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int)                    = nullptr;
+        ncclResult_t (*CommDestroy)(ncclComm_t)                                              = nullptr;
+        ncclResult_t (*CommCount)(const ncclComm_t, int*)                                    = nullptr;
+        ncclResult_t (*CommUserRank)(const ncclComm_t, int*)                                 = nullptr;
+        ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+        ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t)   = nullptr;
+        ncclResult_t (*GroupStart)()                                                         = nullptr;
+        ncclResult_t (*GroupEnd)()                                                           = nullptr;
+        ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t)
+            = nullptr;
+        ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t)
+            = nullptr;
+        const char* (*GetErrorString)(ncclResult_t) = nullptr;
+        bool ok                                     = false;
+    };
+
+    NcclApi& nccl();
+
     // plan->mgpu points at one of two plan kinds; both start with this header
     struct MultiDeviceHeader
     {

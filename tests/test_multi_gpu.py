@@ -54,3 +54,20 @@ def test_single_process_bricks_on_two_devices(gpu, split):
     gpu.cuda.set_device(0)
     err = run_field_case(rf.rocfft_transform_type_complex_forward, 0, [64, 32, 16], 2, gi, go, devices=[0, 1])
     assert err < TOL[0], err
+
+
+def _launch_fields(nproc, case, port):
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mgpu_fields_worker.py"),
+           case]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("case", ["slabs2d_uneven", "real3d", "pencils"])
+def test_multi_process_general_layouts(gpu, case):
+    """Layouts outside the optimised slab plan run as gather -> transform on rank 0 -> scatter over NCCL;
+    with one GPU the same path runs with a single-rank communicator."""
+    _launch_fields(min(2, gpu.cuda.device_count()), case, 29641)
