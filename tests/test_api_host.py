@@ -218,9 +218,9 @@ def test_small_2d_transforms_use_one_fused_kernel(L):
     text = p.describe()
     assert "fft2d_sp_64x64" in text and text.count("  [") == 1, text
     p.destroy()
-    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [27, 81, 5], 2)
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [27, 27, 5], 2)
     text = p.describe()
-    assert "fft2d_dp_27x81" in text and text.count("  [") == 2, text
+    assert "fft2d_dp_27x27" in text and text.count("  [") == 2, text
     p.destroy()
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [64, 100], 10)
     assert "fft2d" not in p.describe()
