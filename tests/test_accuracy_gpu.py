@@ -123,6 +123,21 @@ def cases_2d_single():
     return out
 
 
+def cases_big():
+    """A few transforms of 2^24 points and more: three-kernel 1D decompositions, long column pitches,
+    grids beyond 65535 tiles."""
+    return [Case(C2C_FWD, "single", [1 << 24], 1, IP), Case(C2C_INV, "single", [1 << 22], 3, OOP),
+            Case(C2C_FWD, "single", [4096, 4096], 1, IP), Case(C2C_FWD, "double", [2048, 2048], 2, OOP),
+            Case(C2C_FWD, "single", [256, 256, 256], 1, IP), Case(C2C_INV, "single", [243, 243, 243], 1, OOP),
+            Case(R2C, "single", [1 << 22], 2, OOP), Case(C2R, "single", [4096, 2048], 1, OOP),
+            Case(C2C_FWD, "single", [64], 300000, IP), Case(C2C_FWD, "single", [512, 512, 64], 1, IP)]
+
+
+@pytest.mark.parametrize("case", cases_big(), ids=lambda c: c.ident())
+def test_big_transforms(gpu, case):
+    _run(case)
+
+
 @pytest.mark.parametrize("case", cases_2d_single(), ids=lambda c: c.ident())
 def test_c2c_2d_single_kernel(gpu, case):
     _run(case)
