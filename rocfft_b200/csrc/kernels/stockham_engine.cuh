@@ -219,6 +219,21 @@ namespace b200fft
         }
     }
 
+    // W_N^u from a stepped table: `steps` sub-tables of 256 entries, sub-table s
+    // holding exp(-2 pi i * j * 256^s / N)
+    template <typename T2>
+    __device__ __forceinline__ T2 large_twiddle(const T2* __restrict__ tab, unsigned long long u, int steps)
+    {
+        T2 w = tab[u & 255];
+        for(int s = 1; s < steps; ++s)
+        {
+            u >>= 8;
+            w = cmul(w, tab[256 * s + (u & 255)]);
+        }
+        return w;
+    }
+
+
     // ------------------------------------------------------------------
     // one radix pass
     // ------------------------------------------------------------------
@@ -506,12 +521,25 @@ namespace b200fft
             __syncthreads();
         }
 
+        // Second kernel of a long 1D transform (n = n1 * n2, this kernel: length n2 for each k1): the
+        // N1 x N2 twiddle multiply W_n^(k1 * e) rides on the loads of the variants used there
+        // (reference: large twiddles fused into the SBCC kernels, library/src/device/kernels/common.h:227-301).
+        // aux[2] = stepped table, iaux[2] = its steps; k1 = this transform's index along outer dimension 0.
+        // The value was loaded with parts exchanged for an inverse transform, for which the product
+        // with the forward factor is exactly the exchanged product with the conjugate factor.
+        constexpr bool LT_CAPABLE = !C::COL && C::CIN == COOP_NONE && (C::IOKI == IO_GENERIC || C::COUT == COOP_CFAST);
+        const T2* __restrict__ lt_tab = LT_CAPABLE ? reinterpret_cast<const T2*>(a.aux[2]) : nullptr;
+        const int                lt_steps = (int)a.iaux[2];
+        const unsigned long long lt_k1    = tp.i0_first + (unsigned)c;
         auto g_src = [&](int e) -> T2 {
             T2 v;
             v.x = 0;
             v.y = 0;
             if(valid)
                 v = gload<C>(a.in, ibase, e, inverse);
+            if constexpr(LT_CAPABLE)
+                if(lt_tab)
+                    v = cmul(v, large_twiddle(lt_tab, lt_k1 * (unsigned long long)e, lt_steps));
             return v;
         };
         auto g_dst = [&](int e, T2 v) {

@@ -46,20 +46,6 @@ namespace b200fft
         }
     };
 
-    // W_N^u from a stepped table: `steps` sub-tables of 256 entries, sub-table s
-    // holding exp(-2 pi i * j * 256^s / N)
-    template <typename T2>
-    __device__ __forceinline__ T2 large_twiddle(const T2* __restrict__ tab, unsigned long long u, int steps)
-    {
-        T2 w = tab[u & 255];
-        for(int s = 1; s < steps; ++s)
-        {
-            u >>= 8;
-            w = cmul(w, tab[256 * s + (u & 255)]);
-        }
-        return w;
-    }
-
     template <typename T, int KIND>
     __global__ void __launch_bounds__(256) elementwise_kernel(const __grid_constant__ b200fft_eargs a)
     {

@@ -40,6 +40,9 @@ namespace b200fft
             const void* aux1          = nullptr;
             long long   iaux0         = 0;
             size_t      kernel_length = 0; // pool length when it differs from n (Bluestein: padded length)
+            // second kernel of a long 1D transform: multiply the input by W^(k1 * e), k1 = index of outer[0]
+            const void* lt_tab   = nullptr;
+            int         lt_steps = 0;
         };
 
         inline const b200fft_pool_entry* pool_find(size_t n, int prec, int variant)
@@ -420,6 +423,16 @@ namespace b200fft
                 }
                 if(!kern)
                     kern = pool_find(s.n, prec_, B200FFT_ROW_GEN);
+                // the fused large-twiddle multiply exists in the row variants that serve this stage
+                // and the kernel finds k1 as its index along outer dimension 0, which therefore stays first
+                if(s.lt_tab)
+                {
+                    if(kern && (kern->variant != B200FFT_ROW_GEN && kern->variant != B200FFT_ROW_TOUT))
+                        kern = pool_find(s.n, prec_, B200FFT_ROW_GEN);
+                    if(kern && kern->variant == B200FFT_ROW_TOUT && tiledim != 0)
+                        kern = pool_find(s.n, prec_, B200FFT_ROW_GEN);
+                    tiledim = 0;
+                }
                 if(!kern)
                     throw std::runtime_error("no kernel for length");
 
@@ -572,6 +585,8 @@ namespace b200fft
                 a.aux[0]    = s.aux0 ? s.aux0 : a.aux[0];
                 a.aux[1]    = s.aux1;
                 a.iaux[0]   = s.iaux0;
+                a.aux[2]    = s.lt_tab;
+                a.iaux[2]   = s.lt_steps;
                 st.ntiles   = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];
                 st.in_elem_bytes  = elem_bytes(s.in);
                 st.out_elem_bytes = elem_bytes(s.out);
@@ -616,11 +631,14 @@ namespace b200fft
                 A.inverse = s.inverse;
                 emit_c2c_1d(A);
 
-                // twiddle multiply W_n^(k1*i2) in place on the temp
+                // twiddle multiply W_n^(k1*i2): fused into the loads of stage B when that stage is a single
+                // kernel, otherwise a pass of its own in place on the temp
+                int               steps = 1;
+                std::vector<char> h;
+                host_large_twiddles(s.n, prec_, &steps, h);
+                const bool fuse_tw = pool_has(n2, prec_) && !getenv("ROCFFT_B200_NO_FUSED_LARGE_TWIDDLE");
+                if(!fuse_tw)
                 {
-                    int               steps = 1;
-                    std::vector<char> h;
-                    host_large_twiddles(s.n, prec_, &steps, h);
                     Step st;
                     st.kind       = Step::EW;
                     st.ew_kind    = B200FFT_EW_LARGE_TWIDDLE;
@@ -656,6 +674,11 @@ namespace b200fft
                 B.inverse   = s.inverse;
                 B.use_scale = s.use_scale;
                 B.scale     = s.scale;
+                if(fuse_tw)
+                {
+                    B.lt_tab   = upload(h);
+                    B.lt_steps = steps;
+                }
                 emit_c2c_1d(B);
                 temp_release(mark);
             }
