@@ -133,6 +133,13 @@ def cases_big():
             Case(C2C_FWD, "single", [64], 300000, IP), Case(C2C_FWD, "single", [512, 512, 64], 1, IP)]
 
 
+def test_unfused_large_twiddle_path_agrees(gpu, monkeypatch):
+    """The separate twiddle pass (kept for second stages that are not a single kernel) stays correct."""
+    monkeypatch.setenv("ROCFFT_B200_NO_FUSED_LARGE_TWIDDLE", "1")
+    for case in (Case(C2C_FWD, "single", [65536], 2, IP), Case(C2C_INV, "double", [40000], 2, OOP)):
+        _run(case)
+
+
 @pytest.mark.parametrize("case", cases_big(), ids=lambda c: c.ident())
 def test_big_transforms(gpu, case):
     _run(case)

@@ -225,3 +225,16 @@ def test_small_2d_transforms_use_one_fused_kernel(L):
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [64, 100], 10)
     assert "fft2d" not in p.describe()
     p.destroy()
+
+
+def test_long_1d_transform_is_two_kernels_with_the_twiddles_fused(L, monkeypatch):
+    """n = n1 * n2 beyond the single-kernel lengths: column FFTs, then row FFTs that multiply by W_n^(k1 i2)
+    on load and store transposed; the multiply is a pass of its own only on request."""
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [65536], 4)
+    text = p.describe()
+    assert "steps: 2" in text and "large_twiddle_mul" not in text and "row_tout" in text, text
+    p.destroy()
+    monkeypatch.setenv("ROCFFT_B200_NO_FUSED_LARGE_TWIDDLE", "1")
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [65536], 4)
+    assert "steps: 3" in p.describe() and "large_twiddle_mul" in p.describe()
+    p.destroy()
