@@ -524,23 +524,31 @@ namespace b200fft
         // Second kernel of a long 1D transform (n = n1 * n2, this kernel: length n2 for each k1): the
         // N1 x N2 twiddle multiply W_n^(k1 * e) rides on the loads of the variants used there
         // (reference: large twiddles fused into the SBCC kernels, library/src/device/kernels/common.h:227-301).
-        // aux[2] = stepped table, iaux[2] = its steps; k1 = this transform's index along outer dimension 0.
+        // aux[2] = stepped table of three 256-entry sub-tables; k1 = this transform's index along outer dimension 0.
         // The value was loaded with parts exchanged for an inverse transform, for which the product
         // with the forward factor is exactly the exchanged product with the conjugate factor.
         constexpr bool LT_CAPABLE = !C::COL && C::CIN == COOP_NONE && (C::IOKI == IO_GENERIC || C::COUT == COOP_CFAST);
         const T2* __restrict__ lt_tab = LT_CAPABLE ? reinterpret_cast<const T2*>(a.aux[2]) : nullptr;
-        const int                lt_steps = (int)a.iaux[2];
-        const unsigned long long lt_k1    = tp.i0_first + (unsigned)c;
+        const unsigned long long lt_k1 = tp.i0_first + (unsigned)c;
         auto g_src = [&](int e) -> T2 {
             T2 v;
             v.x = 0;
             v.y = 0;
             if(valid)
                 v = gload<C>(a.in, ibase, e, inverse);
-            if constexpr(LT_CAPABLE)
-                if(lt_tab)
-                    v = cmul(v, large_twiddle(lt_tab, lt_k1 * (unsigned long long)e, lt_steps));
             return v;
+        };
+        // branch-free: the table always has three sub-tables (unused ones hold 1), so that the loads of a
+        // pass still issue back to back
+        auto g_src_lt = [&](int e) -> T2 {
+            T2 v;
+            v.x = 0;
+            v.y = 0;
+            if(valid)
+                v = gload<C>(a.in, ibase, e, inverse);
+            const unsigned long long u = lt_k1 * (unsigned long long)e;
+            const T2 w = cmul(cmul(lt_tab[u & 255], lt_tab[256 + ((u >> 8) & 255)]), lt_tab[512 + ((u >> 16) & 255)]);
+            return cmul(v, w);
         };
         auto g_dst = [&](int e, T2 v) {
             if(valid)
@@ -556,9 +564,19 @@ namespace b200fft
         else if constexpr(SI)
             run_passes<C, 0, true, false>(t, c, sm, tw, s_src, g_dst);
         else if constexpr(SO)
-            run_passes<C, 0, false, true>(t, c, sm, tw, g_src, s_dst);
+        {
+            if(LT_CAPABLE && lt_tab)
+                run_passes<C, 0, false, true>(t, c, sm, tw, g_src_lt, s_dst);
+            else
+                run_passes<C, 0, false, true>(t, c, sm, tw, g_src, s_dst);
+        }
         else
-            run_passes<C, 0, false, false>(t, c, sm, tw, g_src, g_dst);
+        {
+            if(LT_CAPABLE && lt_tab)
+                run_passes<C, 0, false, false>(t, c, sm, tw, g_src_lt, g_dst);
+            else
+                run_passes<C, 0, false, false>(t, c, sm, tw, g_src, g_dst);
+        }
 
         // ---- cooperative store stage ----
         if constexpr(C::COUT == COOP_R2C_POST)

@@ -636,7 +636,25 @@ namespace b200fft
                 int               steps = 1;
                 std::vector<char> h;
                 host_large_twiddles(s.n, prec_, &steps, h);
-                const bool fuse_tw = pool_has(n2, prec_) && !getenv("ROCFFT_B200_NO_FUSED_LARGE_TWIDDLE");
+                // the fused form reads exactly three sub-tables (lengths up to 2^24); shorter tables are
+                // padded with ones
+                const bool fuse_tw = pool_has(n2, prec_) && steps <= 3 && !getenv("ROCFFT_B200_NO_FUSED_LARGE_TWIDDLE");
+                std::vector<char> h3 = h;
+                if(fuse_tw)
+                    for(int sdx = steps; sdx < 3; ++sdx)
+                        for(int j = 0; j < 256; ++j)
+                        {
+                            if(prec_ == 0)
+                            {
+                                const float one[2] = {1.0f, 0.0f};
+                                h3.insert(h3.end(), (const char*)one, (const char*)one + sizeof one);
+                            }
+                            else
+                            {
+                                const double one[2] = {1.0, 0.0};
+                                h3.insert(h3.end(), (const char*)one, (const char*)one + sizeof one);
+                            }
+                        }
                 if(!fuse_tw)
                 {
                     Step st;
@@ -676,8 +694,8 @@ namespace b200fft
                 B.scale     = s.scale;
                 if(fuse_tw)
                 {
-                    B.lt_tab   = upload(h);
-                    B.lt_steps = steps;
+                    B.lt_tab   = upload(h3);
+                    B.lt_steps = 3;
                 }
                 emit_c2c_1d(B);
                 temp_release(mark);
