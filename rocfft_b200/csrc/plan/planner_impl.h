@@ -201,6 +201,13 @@ namespace b200fft
                     double score = -std::fabs(std::log((double)d) - 0.5 * std::log((double)n));
                     if(d > e)
                         score -= 1e-3;
+                    // the second kernel stores transposed: with the cooperative-store variant it writes
+                    // 64-128-byte segments, without it single points (measured ~1 TB/s against ~2.5);
+                    // the first kernel wants a column-tile variant
+                    if(pool_find(e, prec_, B200FFT_ROW_TOUT))
+                        score += 1.0;
+                    if(pool_find(d, prec_, B200FFT_COL_STR))
+                        score += 0.4;
                     if(!found || score > best)
                     {
                         found = true;
