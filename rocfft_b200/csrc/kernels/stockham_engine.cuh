@@ -249,6 +249,33 @@ namespace b200fft
         constexpr bool FULL = (NB % C::TPT) == 0;
         constexpr int TWO = C::FL::tw_offset(P);
 
+        // Long transforms: the stacked table no longer fits the L1 left beside the shared tile, so
+        // twiddle loads come from L2.  Load only the legs j = 1,2,3 and j = 4a and form the others as
+        // products (j = 4a + b): 6 instead of 15 loads for radix 16, 10 instead of 31 for radix 32, at
+        // the cost of one complex multiply per remaining leg (error of one extra rounding, far inside
+        // the bound) — and issue those loads BEFORE the data loads and the barrier, so that their L2
+        // latency overlaps both instead of following the barrier.
+        constexpr bool TW4 = (P > 0) && (C::N >= 8192) && (W >= 8);
+        constexpr int  NA  = TW4 ? (W - 1) / 4 : 1; // legs 4, 8, ...
+        T2 wb[BPT][3], wa[BPT][NA];
+        if constexpr(TW4)
+        {
+#pragma unroll
+            for(int i = 0; i < BPT; ++i)
+            {
+                const int b = t + i * C::TPT;
+                if(FULL || b < NB)
+                {
+                    const int k = b % CH;
+#pragma unroll
+                    for(int b4 = 1; b4 < 4; ++b4)
+                        wb[i][b4 - 1] = tw[TWO + (b4 - 1) * CH + k];
+#pragma unroll
+                    for(int a4 = 1; 4 * a4 < W; ++a4)
+                        wa[i][a4 - 1] = tw[TWO + (4 * a4 - 1) * CH + k];
+                }
+            }
+        }
         T2 x[BPT][W];
 #pragma unroll
         for(int i = 0; i < BPT; ++i)
@@ -272,30 +299,19 @@ namespace b200fft
                 const int k = b % CH;
                 if constexpr(P > 0)
                 {
-                    // Long transforms: the stacked table no longer fits the L1 left beside the
-                    // shared tile, so twiddle loads come from L2.  Load only the legs j = 1,2,3 and
-                    // j = 4a and form the others as products (j = 4a + b): 6 instead of 15 loads
-                    // for radix 16, 10 instead of 31 for radix 32, at the cost of one complex
-                    // multiply per remaining leg (error of one extra rounding, far inside the bound).
-                    constexpr bool TW4 = (C::N >= 8192) && (W >= 8);
                     if constexpr(TW4)
                     {
-                        T2 wb[3];
 #pragma unroll
                         for(int b4 = 1; b4 < 4; ++b4)
-                        {
-                            wb[b4 - 1] = tw[TWO + (b4 - 1) * CH + k];
-                            x[i][b4]   = cmul(x[i][b4], wb[b4 - 1]);
-                        }
+                            x[i][b4] = cmul(x[i][b4], wb[i][b4 - 1]);
 #pragma unroll
                         for(int a4 = 1; 4 * a4 < W; ++a4)
                         {
-                            const T2 wa = tw[TWO + (4 * a4 - 1) * CH + k];
-                            x[i][4 * a4] = cmul(x[i][4 * a4], wa);
+                            x[i][4 * a4] = cmul(x[i][4 * a4], wa[i][a4 - 1]);
 #pragma unroll
                             for(int b4 = 1; b4 < 4; ++b4)
                                 if(4 * a4 + b4 < W)
-                                    x[i][4 * a4 + b4] = cmul(x[i][4 * a4 + b4], cmul(wa, wb[b4 - 1]));
+                                    x[i][4 * a4 + b4] = cmul(x[i][4 * a4 + b4], cmul(wa[i][a4 - 1], wb[i][b4 - 1]));
                         }
                     }
                     else
