@@ -234,6 +234,10 @@ namespace b200fft
     }
 
 
+#ifndef B200FFT_TW4_MIN
+#define B200FFT_TW4_MIN 2048 // shortest transform whose passes factor their twiddle loads
+#endif
+
     // ------------------------------------------------------------------
     // one radix pass
     // ------------------------------------------------------------------
@@ -255,7 +259,7 @@ namespace b200fft
         // the cost of one complex multiply per remaining leg (error of one extra rounding, far inside
         // the bound) — and issue those loads BEFORE the data loads and the barrier, so that their L2
         // latency overlaps both instead of following the barrier.
-        constexpr bool TW4 = (P > 0) && (C::N >= 8192) && (W >= 8);
+        constexpr bool TW4 = (P > 0) && (C::N >= B200FFT_TW4_MIN) && (W >= 8);
         constexpr int  NA  = TW4 ? (W - 1) / 4 : 1; // legs 4, 8, ...
         T2 wb[BPT][3], wa[BPT][NA];
         if constexpr(TW4)
