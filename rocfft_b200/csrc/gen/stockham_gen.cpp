@@ -175,6 +175,9 @@ namespace
         // cluster-of-two column kernels (stockham_colcluster.cuh)
         {"col_cl", 17, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
         {"col_cl_blk", 18, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
+        // odd-length real transforms as one full-length complex kernel
+        {"row_r2c_full", 20, false, "IO_REAL_IN", "IO_HERM_OUT", "COOP_NONE", "COOP_NONE"},
+        {"row_c2r_full", 21, false, "IO_HERM_IN", "IO_REAL_OUT", "COOP_NONE", "COOP_NONE"},
     };
     const int kTmaStages = 3;
     // padded lengths M with a single-kernel Bluestein: 2^k, 3*2^k, 5*2^k
@@ -290,13 +293,15 @@ int main(int argc, char** argv)
                     continue; // per-rank blocks: multi-device slabs need divisible lengths
                 if((v.id == 15 || v.id == 16) && !pow2)
                     continue; // experimental full-line persistent kernel
+                if((v.id == 20 || v.id == 21) && (n % 2 == 0 || n < 3))
+                    continue; // even lengths have the half-length real kernels
                 const bool realv   = v.id == 7 || v.id == 8; // fused even-length real kernels
                 if(realv && n < 4)
                     continue;
                 if(v.id == 9 && !is_bluestein_length(n))
                     continue;
-                if(n > 4096 && v.id != 0 && v.id != 1 && v.id != 9)
-                    continue; // long lengths: plain row kernels and Bluestein only
+                if(n > 4096 && v.id != 0 && v.id != 1 && v.id != 9 && v.id != 20 && v.id != 21)
+                    continue; // long lengths: plain row kernels, Bluestein and the odd-length real kernels only
                 const bool pairv = v.id == 13 || v.id == 14;
                 if(pairv && (prec != 0 || ch.f.size() < 2 || n < 32))
                     continue;

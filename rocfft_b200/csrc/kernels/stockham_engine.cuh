@@ -65,6 +65,12 @@ namespace b200fft
         IO_STRIDED = 1, // interleaved complex, run-time strides
         IO_GENERIC = 2, // interleaved or planar chosen at run time, run-time strides
         IO_BLKOUT  = 3, // like IO_STRIDED, output with a two-level stride along the transform
+        // real transforms computed as full-length complex ones (odd lengths; reference: the odd-length
+        // real kernels of library/src/device/generator and rtc_realcomplex_gen.cpp "r2c_copy"/"c2r_copy" paths)
+        IO_REAL_IN  = 4, // input: real scalars, run-time stride; imaginary part taken as zero
+        IO_HERM_OUT = 5, // output: generic complex store of the points 0..N/2 only
+        IO_HERM_IN  = 6, // input: points 0..N/2 given; point e > N/2 is the conjugate of point N-e
+        IO_REAL_OUT = 7, // output: real part only, run-time stride
     };
     enum CoopKind
     {
@@ -162,6 +168,29 @@ namespace b200fft
         {
             r = reinterpret_cast<const T2*>(v.p[0])[base + (long long)e * v.es];
         }
+        else if constexpr(C::IOKI == IO_REAL_IN)
+        {
+            r.x = reinterpret_cast<const T*>(v.p[0])[base + (long long)e * v.es];
+            r.y = 0;
+        }
+        else if constexpr(C::IOKI == IO_HERM_IN)
+        {
+            const bool      upper = e > C::N / 2;
+            const int       ee    = upper ? C::N - e : e;
+            const long long off   = base + (long long)ee * v.es;
+            if(v.planar)
+            {
+                r.x = reinterpret_cast<const T*>(v.p[0])[off];
+                r.y = reinterpret_cast<const T*>(v.p[1])[off];
+            }
+            else
+                r = reinterpret_cast<const T2*>(v.p[0])[off];
+            if(upper)
+                r.y = -r.y;
+            // the imaginary parts of DC and Nyquist carry no information
+            if(ee == 0 || (C::N % 2 == 0 && ee == C::N / 2))
+                r.y = 0;
+        }
         else
         {
             const long long off = base + (long long)e * v.es;
@@ -205,6 +234,24 @@ namespace b200fft
         else if constexpr(C::IOKO == IO_BLKOUT)
         {
             *blk_address<T2>(v, base, e) = val;
+        }
+        else if constexpr(C::IOKO == IO_REAL_OUT)
+        {
+            reinterpret_cast<T*>(v.p[0])[base + (long long)e * v.es] = val.x;
+        }
+        else if constexpr(C::IOKO == IO_HERM_OUT)
+        {
+            if(e <= C::N / 2)
+            {
+                const long long off = base + (long long)e * v.es;
+                if(v.planar)
+                {
+                    reinterpret_cast<T*>(v.p[0])[off] = val.x;
+                    reinterpret_cast<T*>(v.p[1])[off] = val.y;
+                }
+                else
+                    reinterpret_cast<T2*>(v.p[0])[off] = val;
+            }
         }
         else
         {

@@ -47,6 +47,11 @@ typedef enum b200fft_variant
     // memory (stockham_colcluster.cuh); power-of-two lengths
     B200FFT_COL_CL     = 17,
     B200FFT_COL_CL_BLK = 18,
+    // 19: whole small 2D transforms (B200FFT_2D_SINGLE, separate table below)
+    // real transforms of odd length as one full-length complex kernel: real rows in / Hermitian
+    // half out, and Hermitian half in (rebuilt by conjugate symmetry) / real rows out
+    B200FFT_ROW_R2C_FULL = 20,
+    B200FFT_ROW_C2R_FULL = 21,
 } b200fft_variant;
 
 typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);

@@ -1008,6 +1008,26 @@ namespace b200fft
                     st.note           = "r2c_even_post";
                     core_.steps.push_back(st);
                 }
+                else if(pool_find(n0, prec_, B200FFT_ROW_R2C_FULL) && !getenv("ROCFFT_B200_NO_REAL_FULL"))
+                {
+                    // odd length: one full-length complex kernel that reads the real row (imaginary part
+                    // zero) and stores the points 0..n0/2 — one pass instead of copy, transform, copy
+                    Stage s;
+                    s.n  = n0;
+                    s.is = in.stride[0];
+                    s.os = out.stride[0];
+                    for(size_t k = 0; k < o_in.size(); ++k)
+                        s.outer.push_back({o_in[k].len, o_in[k].is, o_in[k].os});
+                    s.in            = in.buf;
+                    s.in.planar     = false;
+                    s.out           = out.buf;
+                    s.use_scale     = use_scale;
+                    s.scale         = scale;
+                    s.force_variant = B200FFT_ROW_R2C_FULL;
+                    drop_unit_dims(s.outer);
+                    emit_tile(s);
+                    core_.steps.back().in_elem_bytes = rsize_;
+                }
                 else
                 {
                     const size_t total = temp_outer_strides(o_in, n0, ts);
@@ -1131,6 +1151,27 @@ namespace b200fft
                     s.use_scale  = use_scale;
                     s.scale      = scale;
                     emit_c2c_1d(s);
+                }
+                else if(pool_find(n0, prec_, B200FFT_ROW_C2R_FULL) && !getenv("ROCFFT_B200_NO_REAL_FULL"))
+                {
+                    // odd length: one full-length complex kernel that rebuilds the upper half of the
+                    // spectrum by conjugate symmetry on load and stores the real parts
+                    Stage s;
+                    s.n  = n0;
+                    s.is = in.stride[0];
+                    s.os = out.stride[0];
+                    for(size_t k = 0; k < o_io.size(); ++k)
+                        s.outer.push_back({o_io[k].len, o_io[k].is, o_io[k].os});
+                    s.in            = in.buf;
+                    s.out           = out.buf;
+                    s.out.planar    = false;
+                    s.inverse       = true;
+                    s.use_scale     = use_scale;
+                    s.scale         = scale;
+                    s.force_variant = B200FFT_ROW_C2R_FULL;
+                    drop_unit_dims(s.outer);
+                    emit_tile(s);
+                    core_.steps.back().out_elem_bytes = rsize_;
                 }
                 else
                 {

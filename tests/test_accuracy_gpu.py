@@ -170,6 +170,15 @@ def cases_real():
         out.append(Case(C2R, prec, [30], 3, OOP, HI, RE, [2], [3], 40, 100))
         out.append(Case(R2C, prec, [64], 3, OOP, RE, HI, [1], [1], 66, 33, [2], [1]))
         out.append(Case(R2C, prec, [64], 3, OOP, RE, HI, [1], [1], 65, 33, [1], [1]))  # odd distance: general path
+        # odd lengths: one full-length complex kernel each way, in every layout flavour
+        out.append(Case(R2C, prec, [125], 3, OOP, RE, HP))
+        out.append(Case(C2R, prec, [125], 3, OOP, HP, RE))
+        out.append(Case(R2C, prec, [27], 3, OOP, RE, HI, [2], [3], 60, 50))
+        out.append(Case(C2R, prec, [27], 3, OOP, HI, RE, [3], [2], 50, 60))
+        out.append(Case(R2C, prec, [243], 700, OOP, scale=0.5))
+        out.append(Case(C2R, prec, [3125], 5, IP, scale=1.0 / 3125))
+        out.append(Case(R2C, prec, [81, 27], 3, IP))
+        out.append(Case(C2R, prec, [15, 15, 15], 2, OOP))
         out.append(Case(C2R, prec, [1000], 4, OOP, scale=1e-3))
         out.append(Case(R2C, prec, [1000], 4, OOP, scale=2.0))
     return out
