@@ -2,9 +2,10 @@
 
 torch.distributed is used only as plumbing: to ship the NCCL unique id between
 ranks and for barriers / max-over-ranks reductions of timings.  The transform
-itself — local FFT passes, the packed all-to-all over NCCL, the overlap
-schedule — lives in librocfft.so behind the field / brick API of rocfft.h
-(reference call sequence: clients/samples/mpi/rocfft_mpi_example.cpp).
+itself — local FFT passes whose stores land directly in the peer GPUs' buffers
+over NVLink (or, as an option, a chunked NCCL send/recv exchange) — lives in
+librocfft.so behind the field / brick API of rocfft.h (reference call
+sequence: clients/samples/mpi/rocfft_mpi_example.cpp).
 """
 from __future__ import annotations
 
@@ -127,15 +128,20 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
     stream = torch.cuda.Stream()
     fft.attach(torch, stream.cuda_stream)
     lz = nz // world
+    from bench import ClockSampler, SampledCheck3D, headline_config
+    verify = not getattr(args, "no_verify", False)
+    chk = SampledCheck3D((nz, ny, nx), rank * lz, lz, world=world, rank=rank) if verify else None
     rng = np.random.default_rng(5 + rank)
     x = torch.empty(lz * ny * nx, dtype=torch.complex64, device="cuda")
-    chunk = 1 << 24
+    chunk = 1 << 24  # 16 XY planes
     for s in range(0, x.numel(), chunk):
         n = min(chunk, x.numel() - s)
         a = np.empty(n, dtype=np.complex64)
         a.real = rng.random(n, dtype=np.float32) - 0.5
         a.imag = rng.random(n, dtype=np.float32) - 0.5
         x[s:s + n].copy_(torch.from_numpy(a))
+        if chk is not None:
+            chk.feed(rank * lz + s // (ny * nx), a.reshape(-1, ny, nx))
     L = rf.lib()
     L.b200fft_launch_count.restype = ctypes.c_ulonglong
 
@@ -144,7 +150,18 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
         if st != 0:
             raise RuntimeError(f"rocfft_execute failed: {st}")
 
-    from bench import ClockSampler
+    # the first transform runs on the freshly seeded slabs and is checked before anything is timed
+    verdict = None
+    if chk is not None:
+        with torch.cuda.stream(stream):
+            step()
+        torch.cuda.synchronize()
+        verdict = chk.finish(x, scale, dist=dist, torch=torch)
+        if not verdict["ok"]:
+            if rank == 0:
+                print(json.dumps({"verify": verdict, "n_gpus": world}), flush=True)
+            raise SystemExit(f"verification FAILED on {world} GPUs: {verdict}")
+
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             step()
@@ -237,16 +254,17 @@ def bench_main(args, METRIC, UNIT, HEADLINE, peak, peak_src):
         line = {"metric": METRIC, "value": flops / ms_max / 1e6, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": HEADLINE, "lengths": [nx, ny, nz], "decomposition": f"z-slabs x{world}",
-                           "placement": "inplace", "exchange": ("NCCL grouped send/recv, 2 global transposes" if os.environ.get("ROCFFT_B200_MGPU_NCCL")
-                                        else "peer stores over NVLink fused into FFT passes A and B, 2 global transposes"),
-                           "l2": "slab >> L2, no flush needed"},
+                "config": headline_config(world),
+                "exchange": ("NCCL grouped send/recv, 2 global transposes" if os.environ.get("ROCFFT_B200_MGPU_NCCL")
+                             else "peer stores over NVLink fused into FFT passes A and B, 2 global transposes"),
                 "roofline": {"bound": "nvlink", "achieved": a2a_bytes / ms_max / 1e6, "peak": 770.0,
                              "peak_source": "measured peer copy per direction", "unit": "GB/s",
                              "frac": a2a_bytes / ms_max / 1e6 / 770.0, "traffic": None,
                              "note": "bytes each GPU must send over NVLink per transform / step time",
                              "local_hbm_bytes_per_gpu": per_gpu_bytes},
                 "clocks": cs.summary(), "gpu_launches": launches, "host_enqueue_ms_per_step": host_ms}
+        if verdict is not None:
+            line["verify"] = verdict
         if e2e:
             line["e2e"] = e2e
         print(json.dumps(line), flush=True)
