@@ -58,14 +58,16 @@ ROCFFT_EXPORT rocfft_status b200fft_nccl_comm_destroy(void* comm);
  *
  * Single precision, interleaved, unit stride, `batch` rows of `length` points
  * back to back; in == out is allowed.  `length` must be a power of two from 256
- * to 1048576 and length * batch * 8 bytes must not exceed 4 MiB
+ * to 524288 and length * batch * 8 bytes must not exceed 4 MiB
  * (rocfft_status_invalid_arg_value otherwise): the intermediate array lives in a
  * 4 MiB + 64 KiB __device__ array inside the library image, which every GPU
  * that loads the library holds until the process exits.  `stream` is a
  * cudaStream_t.  The first call on a device, and the first call after `length`
- * changes, copies small tables synchronously — make that call before any
- * stream capture begins.  All calls share the array: calls that overlap on the
- * GPU race, so serialise them. */
+ * changes, rewrites small tables in that array: it waits for `stream` to drain,
+ * copies the tables on `stream` and waits again — make that call before any
+ * stream capture begins; calls that keep `length` never synchronise.  All calls
+ * share the array: calls that overlap on the GPU (other streams, other host
+ * threads) race, so serialise them. */
 ROCFFT_EXPORT rocfft_status b200fft_c2c_1d_static_scratch(
     const void* in, void* out, size_t length, size_t batch, int inverse, void* stream);
 

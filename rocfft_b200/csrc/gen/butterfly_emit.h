@@ -141,8 +141,8 @@ namespace gen
             std::string c   = lit(std::cos(ang));
             std::string s   = lit(std::sin(ang));
             // (ar + i ai)(c - i s) = (ar c + ai s) + i (ai c - ar s)
-            return {def(a.re + " * " + c + " + " + a.im + " * " + s),
-                    def(a.im + " * " + c + " - " + a.re + " * " + s)};
+            return {def("madd(" + a.re + ", " + c + ", " + a.im + ", " + s + ")"),
+                    def("msub(" + a.im + ", " + c + ", " + a.re + ", " + s + ")")};
         }
 
         static int smallest_prime(int n)
@@ -219,15 +219,16 @@ namespace gen
             }
             for(int k = 1; k <= h; ++k)
             {
+                // sums of products as chains of fused multiply-adds
                 std::string are = x[0].re, aim = x[0].im, bre, bim;
                 for(int j = 1; j <= h; ++j)
                 {
                     long double ang = 2.0L * pi * (long double)((j * k) % p) / (long double)p;
                     std::string c = lit(std::cos(ang)), s = lit(std::sin(ang));
-                    are += " + " + c + " * " + a[j].re;
-                    aim += " + " + c + " * " + a[j].im;
-                    bre += (j > 1 ? " + " : "") + s + " * " + b[j].re;
-                    bim += (j > 1 ? " + " : "") + s + " * " + b[j].im;
+                    are = "bfma(" + c + ", " + a[j].re + ", " + are + ")";
+                    aim = "bfma(" + c + ", " + a[j].im + ", " + aim + ")";
+                    bre = j > 1 ? "bfma(" + s + ", " + b[j].re + ", " + bre + ")" : s + " * " + b[j].re;
+                    bim = j > 1 ? "bfma(" + s + ", " + b[j].im + ", " + bim + ")" : s + " * " + b[j].im;
                 }
                 Cv A{def(are), def(aim)}, B{def(bre), def(bim)};
                 // X[k] = A - i B,  X[p-k] = A + i B

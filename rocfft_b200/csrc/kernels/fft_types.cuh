@@ -58,6 +58,87 @@ namespace b200fft
         return r;
     }
 
+    // Arithmetic helpers the generated butterflies are written in, so that the same straight-line
+    // code serves scalars and the packed pairs below: a * b + c, a * c + b * s, a * c - b * s.
+    template <typename T>
+    B200FFT_DEVICE T bfma(const T a, const T b, const T c)
+    {
+        return a * b + c;
+    }
+    template <typename T>
+    B200FFT_DEVICE T madd(const T a, const T c, const T b, const T s)
+    {
+        return a * c + b * s;
+    }
+    template <typename T>
+    B200FFT_DEVICE T msub(const T a, const T c, const T b, const T s)
+    {
+        return a * c - b * s;
+    }
+
+#if defined(__CUDACC__)
+    // Two single-precision values that travel through the packed fp32 instructions of sm_100
+    // (add / mul / fma on an aligned register pair: one issue slot for two lanes).  The kernels
+    // that use it put the SAME component of TWO independent transforms into one pair — real parts
+    // of columns a and b in one pk2, imaginary parts in another — so the generated butterflies run
+    // unchanged on `pk2` scalars and every instruction serves two transforms, with no shuffling
+    // between the halves of a pair.
+    struct pk2
+    {
+        float2 v;
+        pk2() = default;
+        __device__ __forceinline__ pk2(float2 a)
+            : v(a)
+        {
+        }
+        __device__ __forceinline__ pk2(float a, float b)
+            : v(make_float2(a, b))
+        {
+        }
+        // literal constants of the butterflies: the same value in both lanes
+        __device__ __forceinline__ explicit pk2(double c)
+            : v(make_float2((float)c, (float)c))
+        {
+        }
+    };
+    __device__ __forceinline__ pk2 operator+(const pk2 a, const pk2 b)
+    {
+        return pk2(__fadd2_rn(a.v, b.v));
+    }
+    __device__ __forceinline__ pk2 operator-(const pk2 a, const pk2 b)
+    {
+        return pk2(__ffma2_rn(b.v, make_float2(-1.0f, -1.0f), a.v));
+    }
+    __device__ __forceinline__ pk2 operator*(const pk2 a, const pk2 b)
+    {
+        return pk2(__fmul2_rn(a.v, b.v));
+    }
+    __device__ __forceinline__ pk2 operator-(const pk2 a)
+    {
+        return pk2(__fmul2_rn(a.v, make_float2(-1.0f, -1.0f)));
+    }
+    template <>
+    __device__ __forceinline__ pk2 bfma<pk2>(const pk2 a, const pk2 b, const pk2 c)
+    {
+        return pk2(__ffma2_rn(a.v, b.v, c.v));
+    }
+    template <>
+    __device__ __forceinline__ pk2 madd<pk2>(const pk2 a, const pk2 c, const pk2 b, const pk2 s)
+    {
+        return pk2(__ffma2_rn(a.v, c.v, __fmul2_rn(b.v, s.v)));
+    }
+    template <>
+    __device__ __forceinline__ pk2 msub<pk2>(const pk2 a, const pk2 c, const pk2 b, const pk2 s)
+    {
+        return pk2(__ffma2_rn(a.v, c.v, __fmul2_rn(b.v, make_float2(-s.v.x, -s.v.y))));
+    }
+    // complex value whose parts are packed pairs: two complex numbers, structure-of-arrays
+    struct pk2c
+    {
+        pk2 x, y;
+    };
+#endif
+
     // forward DFT of W points held in registers, natural order in and out;
     // specialisations come from the generated header
     template <int W, typename T2>

@@ -20,13 +20,15 @@
 //
 // Limits and rules (also stated in the header):
 //   - single precision, interleaved complex, unit stride, rows back to back;
-//   - length = N1 * N2 with both factors powers of two between 16 and 1024
-//     (lengths 256 ... 1048576);
-//   - length * batch * 8 bytes <= B200FFT_STATIC_SCRATCH_BYTES (4 MiB);
-//     anything larger is refused with rocfft_status_invalid_arg_value;
+//   - length = N1 * N2 with both factors powers of two between 16 and 1024,
+//     and length * batch * 8 bytes <= B200FFT_STATIC_SCRATCH_BYTES (4 MiB):
+//     lengths 256 ... 524288 (the longest row that fits the array); anything
+//     else is refused with rocfft_status_invalid_arg_value;
 //   - the first call on a device, and the first call after the length
-//     changes, copies small tables to the device synchronously: make that
-//     call before starting any stream capture;
+//     changes, rewrites the small tables: it waits for `stream` to drain (work
+//     queued there earlier may still read the old tables), copies the new tables
+//     on `stream` and waits again.  Make that call before starting any stream
+//     capture.  Calls that keep the length do not synchronise;
 //   - all calls share the one scratch array, which keeps the previous call's
 //     contents (nothing in it needs to start at zero: every call overwrites
 //     what it reads).  Calls that overlap on the GPU (different streams, or
@@ -105,28 +107,44 @@ extern "C" ROCFFT_EXPORT rocfft_status b200fft_c2c_1d_static_scratch(
     }
     if(st.table_len != length)
     {
-        st.k1 = find_kernel(n1, B200FFT_COL_STR);
-        st.k2 = find_kernel(n2, B200FFT_ROW_TOUT);
-        if(!st.k1 || !st.k2)
+        // everything is prepared in locals and committed to the per-device state only after the
+        // last step succeeded, so that a failure leaves the previous length fully usable
+        const b200fft_pool_entry* k1 = find_kernel(n1, B200FFT_COL_STR);
+        const b200fft_pool_entry* k2 = find_kernel(n2, B200FFT_ROW_TOUT);
+        if(!k1 || !k2)
             return rocfft_status_failure;
         std::vector<char> t1, t2, tl;
-        b200fft::host_stacked_twiddles((int)n1, st.k1->factors, st.k1->nfactors, 0, t1);
-        b200fft::host_stacked_twiddles((int)n2, st.k2->factors, st.k2->nfactors, 0, t2);
-        b200fft::host_large_twiddles(length, 0, &st.large_steps, tl);
-        auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
-        st.off_tw1   = B200FFT_STATIC_SCRATCH_BYTES;
-        st.off_tw2   = st.off_tw1 + up(t1.size());
-        st.off_large = st.off_tw2 + up(t2.size());
-        if(st.off_large + tl.size() > B200FFT_STATIC_SCRATCH_BYTES + B200FFT_STATIC_TABLE_BYTES)
+        int               large_steps = 1;
+        b200fft::host_stacked_twiddles((int)n1, k1->factors, k1->nfactors, 0, t1);
+        b200fft::host_stacked_twiddles((int)n2, k2->factors, k2->nfactors, 0, t2);
+        b200fft::host_large_twiddles(length, 0, &large_steps, tl);
+        auto         up        = [](size_t v) { return (v + 255) & ~size_t(255); };
+        const size_t off_tw1   = B200FFT_STATIC_SCRATCH_BYTES;
+        const size_t off_tw2   = off_tw1 + up(t1.size());
+        const size_t off_large = off_tw2 + up(t2.size());
+        if(off_large + tl.size() > B200FFT_STATIC_SCRATCH_BYTES + B200FFT_STATIC_TABLE_BYTES)
             return rocfft_status_failure;
-        // small synchronous copies into the static array: no allocation involved
-        if(cudaMemcpy(st.base + st.off_tw1, t1.data(), t1.size(), cudaMemcpyHostToDevice) != cudaSuccess
-           || cudaMemcpy(st.base + st.off_tw2, t2.data(), t2.size(), cudaMemcpyHostToDevice) != cudaSuccess
-           || cudaMemcpy(st.base + st.off_large, tl.data(), tl.size(), cudaMemcpyHostToDevice) != cudaSuccess)
+        // Kernels of an earlier call queued on this stream may still read the old tables, and a
+        // blocking copy on the legacy stream would not be ordered against a non-blocking stream:
+        // drain the caller's stream, copy on it, and drain again (the host vectors go out of scope).
+        // No allocation is involved: the destination is the static array.
+        if(cudaStreamSynchronize(s) != cudaSuccess)
             return rocfft_status_failure;
-        st.table_len = length;
-        st.n1        = n1;
-        st.n2        = n2;
+        st.table_len = 0; // the table region is about to change: not valid for any length until committed
+        if(cudaMemcpyAsync(st.base + off_tw1, t1.data(), t1.size(), cudaMemcpyHostToDevice, s) != cudaSuccess
+           || cudaMemcpyAsync(st.base + off_tw2, t2.data(), t2.size(), cudaMemcpyHostToDevice, s) != cudaSuccess
+           || cudaMemcpyAsync(st.base + off_large, tl.data(), tl.size(), cudaMemcpyHostToDevice, s) != cudaSuccess
+           || cudaStreamSynchronize(s) != cudaSuccess)
+            return rocfft_status_failure;
+        st.k1          = k1;
+        st.k2          = k2;
+        st.off_tw1     = off_tw1;
+        st.off_tw2     = off_tw2;
+        st.off_large   = off_large;
+        st.large_steps = large_steps;
+        st.n1          = n1;
+        st.n2          = n2;
+        st.table_len   = length;
     }
 
     char* T = st.base; // intermediate array [batch][k1][i2]
