@@ -172,9 +172,9 @@ namespace
         // paired-column kernels (stockham_colpair.cuh), single precision only
         {"col_pair", 13, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
         {"col_pair_blk", 14, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
-        // persistent full-line column kernels (stockham_colwide.cuh)
-        {"col_wide", 15, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
-        {"col_wide_blk", 16, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
+        // persistent TMA-fed full-line column kernels (stockham_colstream.cuh)
+        {"col_tma", 15, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
+        {"col_tma_blk", 16, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
         // cluster-of-two column kernels (stockham_colcluster.cuh)
         {"col_cl", 17, true, "IO_STRIDED", "IO_STRIDED", "COOP_NONE", "COOP_NONE"},
         {"col_cl_blk", 18, true, "IO_STRIDED", "IO_BLKOUT", "COOP_NONE", "COOP_NONE"},
@@ -294,8 +294,9 @@ int main(int argc, char** argv)
                     continue; // column-in / row-out
                 if(v.id == 6 && (n % 2 != 0))
                     continue; // per-rank blocks: multi-device slabs need divisible lengths
-                if((v.id == 15 || v.id == 16) && !pow2)
-                    continue; // experimental full-line persistent kernel
+                const bool streamv = v.id == 15 || v.id == 16;
+                if(streamv && (!pow2 || n < 256 || n > 1024))
+                    continue; // persistent TMA-fed column kernel: a 128-byte-wide tile must fit shared memory
                 if((v.id == 20 || v.id == 21) && (n % 2 == 0 || n < 3))
                     continue; // even lengths have the half-length real kernels
                 const bool realv   = v.id == 7 || v.id == 8; // fused even-length real kernels
@@ -315,7 +316,7 @@ int main(int argc, char** argv)
                 const bool push = clv && prec == 0 && pow2 && n >= 64 && n <= 1024;
                 int        kt   = tpt; // threads per transform and factors of this kernel
                 std::vector<int> kf = ch.f;
-                if(push)
+                if(push || streamv)
                 {
                     int w0 = 8;
                     while(w0 * w0 < n)
@@ -325,7 +326,7 @@ int main(int argc, char** argv)
                 }
                 if(clv && !push && ((n & (n - 1)) != 0 || n < 64 || tpt % 2))
                     continue;
-                const bool widev = v.id == 15 || v.id == 16 || clv;
+                const bool widev = clv;
                 if(widev && !push && (tuned || ch.f.size() < 2 || n < 32 || tpt * 8 > 1024 || ch.f[0] != ept))
                     continue;
                 if(widev && !push)
@@ -410,17 +411,16 @@ int main(int argc, char** argv)
                     if(sm > 200 * 1024 || tpt * 4 > 1024)
                         continue;
                 }
-                else if(widev)
+                else if(streamv)
                 {
+                    // stage (n rows x 128 bytes) + half-tile exchange buffer + alignment slack
                     tpb = 128 / esz;
-                    sm  = (size_t)n * 128 + (size_t)(n + (n >> 4) + 1) * 64;
-                    if(sm > 225 * 1024)
-                        continue;
+                    sm  = 1024 + (size_t)n * 128 + (size_t)(n + (n >> 5) + 1) * 64 + 16;
                 }
                 else if(sm > smem_cap)
                     continue;
-                const int threads = clv ? kt * 4 : widev ? tpt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
-                int       minb    = std::max(1, 65536 / (threads * (push ? 170 : (pairv || clv) ? 128 : regcap)));
+                const int threads = clv ? kt * 4 : streamv ? kt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
+                int       minb    = std::max(1, 65536 / (threads * (push ? 170 : streamv ? 255 : (pairv || clv) ? 128 : regcap)));
                 if(push)
                     minb = std::min(minb, 4);
                 if(sm)
@@ -548,7 +548,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colwide.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_colstream.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -564,7 +564,7 @@ int main(int argc, char** argv)
         else if(k.variant == 13 || k.variant == 14)
             o << "launch_colpair_kernel<" << k.cfg << ", " << (k.variant == 14 ? "true" : "false") << ">";
         else if(k.variant == 15 || k.variant == 16)
-            o << "launch_colwide_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ">";
+            o << "launch_colstream_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ">";
         else if(k.variant == 17 || k.variant == 18)
             o << (k.push ? "launch_colpush_kernel<" : "launch_colcluster_kernel<") << k.cfg << ", 2, "
               << (k.variant == 18 ? "true" : "false") << ">";

@@ -92,7 +92,7 @@ namespace b200fft
     cudaError_t launch_2d_kernel(const b200fft_kargs& a, unsigned long long nimages, cudaStream_t stream)
     {
         using F                   = Fused2D<C0, C1>;
-        static bool attr_done[64] = {};
+        static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int         dev           = 0;
         cudaGetDevice(&dev);
         auto kern = stockham_2d_kernel<C0, C1, MINB>;

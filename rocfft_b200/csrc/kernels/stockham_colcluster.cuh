@@ -25,7 +25,7 @@
 // 8 double complex), strides multiples of 16 bytes, 16-byte aligned bases.
 // Inverse transforms are conj(FFT(conj x)).
 #pragma once
-#include "stockham_colwide.cuh"
+#include "stockham_colcommon.cuh"
 
 namespace b200fft
 {
@@ -271,7 +271,7 @@ namespace b200fft
     cudaError_t launch_colcluster_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
         using CC                  = ColCluster<C, CL>;
-        static bool attr_done[64] = {};
+        static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int         dev           = 0;
         cudaGetDevice(&dev);
         auto kern = stockham_colcluster_kernel<C, CL, BLK>;

@@ -251,7 +251,7 @@ namespace b200fft
     cudaError_t launch_colpair_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
         using CPK                 = ColPair<C>;
-        static bool attr_done[64] = {};
+        static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int         dev           = 0;
         cudaGetDevice(&dev);
         auto kern = stockham_colpair_kernel<C, BLK>;

@@ -49,6 +49,10 @@ namespace b200fft
         {
             asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
         }
+        __device__ __forceinline__ void cluster_arrive_release()
+        {
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        }
         __device__ __forceinline__ void cluster_wait()
         {
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -233,9 +237,11 @@ namespace b200fft
                         r[v][i * PN::W + j] = tmp[v];
                 }
             }
-            // the buffer may be refilled once every CTA has got here; waited for before the next push
+            // the buffer may be refilled once every CTA has got here; waited for before the next push.
+            // Release semantics order the shared-memory reads above before the peers' next pushes
+            // into the same slots (only kernels of three or more passes get here).
             if constexpr(P + 1 < C::NPASS - 1)
-                ptx::cluster_arrive_relaxed();
+                ptx::cluster_arrive_release();
             colpush_from<C, CL, P + 1, BLK>(rank, tl, u, sm, bar, win, wbar, tw, r, a, gout, obase, sx, sy);
         }
     }
@@ -316,7 +322,7 @@ namespace b200fft
     cudaError_t launch_colpush_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
         using CC                  = ColPush<C, CL>;
-        static bool attr_done[64] = {};
+        static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int         dev           = 0;
         cudaGetDevice(&dev);
         auto kern = stockham_colpush_kernel<C, CL, BLK>;

@@ -1,0 +1,484 @@
+// Persistent column-tile Stockham kernel fed by the tensor copy engine (TMA).
+//
+// Role in the reference: CS_KERNEL_STOCKHAM_BLOCK_CC
+// (library/src/device/generator/stockham_gen_cc.h; chosen for the higher
+// dimensions of 2D/3D transforms, library/src/tree_node_1D.cpp:1102-1112): FFTs
+// along a strided dimension, a tile of adjacent columns per workgroup.
+//
+// Shape.  A tile is N rows x 128 bytes (16 single or 8 double complex columns):
+// strided tiles only move at the full HBM rate when their row segments are whole
+// 128-byte lines.  One persistent CTA per resident slot walks over the tiles:
+//
+//   load     one elected thread issues cp.async.bulk.tensor box loads (boxes of up to
+//            256 rows x 128 bytes, described by a tensor map of the caller's array;
+//            no multicast, no cluster) that land in a shared-memory stage and
+//            complete on an mbarrier — no thread holds registers for data in flight;
+//   pass 0   every thread moves its points from the stage into registers; after one
+//            barrier the stage is free and the load of the CTA's NEXT tile is issued,
+//            so it is in flight during everything that follows;
+//   exchange between passes the tile changes owner through a shared buffer that holds
+//            half of it: real parts first, imaginary parts second;
+//   store    the last pass writes its results from registers straight to global
+//            memory as 16-byte units (whole 128-byte lines per row).
+//
+// Single precision runs TWO adjacent columns per thread in packed form (pk2c: real
+// parts of both columns in one aligned register pair, imaginary parts in another), so
+// every butterfly instruction is a packed fp32 instruction serving two transforms; a
+// 16-byte unit of a row is exactly one such pair of complex values.  Double precision
+// runs one column per thread.  Either way a value's component is 8 bytes, which is
+// what the exchange buffer is made of.
+//
+// Requirements (planner / launch layer): power-of-two length, unit stride across
+// columns on both sides, column count a multiple of the tile width, input strides
+// positive multiples of 16 bytes, 16-byte aligned bases.  Inverse transforms are
+// conj(FFT(conj x)).  Every mbarrier wait is bounded; when one gives up, the whole CTA
+// learns of it at the next barrier, raises the plan's device error flag (aux[3]), waits
+// (bounded again) for the copy that is still in flight and leaves.
+#pragma once
+#include "stockham_colpush.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <utility>
+
+namespace b200fft
+{
+    namespace ptx
+    {
+        // 4D tiled box load, global -> shared, completing on an mbarrier of this CTA (no multicast)
+        __device__ __forceinline__ void
+            tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar)
+        {
+            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, "
+                         "%4, %5}], [%6];" ::"r"(smem_u32(smem_dst)),
+                         "l"(map),
+                         "r"(c0),
+                         "r"(c1),
+                         "r"(c2),
+                         "r"(c3),
+                         "r"(smem_u32(bar))
+                         : "memory");
+        }
+    }
+
+    // value representation inside the kernel: P = one 8-byte component
+    template <typename T>
+    struct StreamVal;
+    template <>
+    struct StreamVal<float>
+    {
+        using P                  = pk2;
+        using C2                 = pk2c;
+        using U                  = float4;
+        static constexpr int VEC = 2; // columns per thread
+        __device__ static __forceinline__ C2 unpack(const float4 v, float sgn)
+        {
+            C2 r;
+            r.x = pk2(v.x, v.z);
+            r.y = pk2(v.y * sgn, v.w * sgn);
+            return r;
+        }
+        __device__ static __forceinline__ float4 pack(const C2 c, float sx, float sy)
+        {
+            return make_float4(c.x.v.x * sx, c.y.v.x * sy, c.x.v.y * sx, c.y.v.y * sy);
+        }
+        // c * w for a scalar twiddle w
+        __device__ static __forceinline__ C2 twmul(const C2 c, const float2 w)
+        {
+            const float2 wx = make_float2(w.x, w.x), wy = make_float2(w.y, w.y), nwy = make_float2(-w.y, -w.y);
+            C2           r;
+            r.x = pk2(__ffma2_rn(c.x.v, wx, __fmul2_rn(c.y.v, nwy)));
+            r.y = pk2(__ffma2_rn(c.x.v, wy, __fmul2_rn(c.y.v, wx)));
+            return r;
+        }
+    };
+    template <>
+    struct StreamVal<double>
+    {
+        using P                  = double;
+        using C2                 = double2;
+        using U                  = double2;
+        static constexpr int VEC = 1;
+        __device__ static __forceinline__ C2 unpack(const double2 v, double sgn)
+        {
+            return make_double2(v.x, v.y * sgn);
+        }
+        __device__ static __forceinline__ double2 pack(const C2 c, double sx, double sy)
+        {
+            return make_double2(c.x * sx, c.y * sy);
+        }
+        __device__ static __forceinline__ C2 twmul(const C2 c, const double2 w)
+        {
+            return cmul(c, w);
+        }
+    };
+
+    template <class C>
+    struct ColStream
+    {
+        using T                          = typename C::T;
+        using SV                         = StreamVal<T>;
+        using P                          = typename SV::P;
+        using C2                         = typename SV::C2;
+        using U                          = typename SV::U;
+        static constexpr int VEC         = SV::VEC;
+        static constexpr int UNITS       = 8; // 16-byte units per 128-byte row segment
+        static constexpr int COLS        = UNITS * VEC;
+        static constexpr int THREADS     = C::TPT * UNITS;
+        static constexpr int EPT         = C::N / C::TPT;
+        static constexpr int BOX_ROWS    = C::N < 256 ? C::N : 256;
+        static constexpr int NBOX        = C::N / BOX_ROWS;
+        static constexpr unsigned STAGE_BYTES = (unsigned)C::N * 128u;
+        static constexpr int      XROWS       = C::N + (C::N >> 5) + 1; // one pad row per 32 keeps both passes conflict-free
+        static constexpr size_t   XCHG_BYTES  = C::NPASS > 1 ? (size_t)XROWS * UNITS * 8 : 0;
+        static constexpr size_t   SMEM_BYTES  = 1024 + STAGE_BYTES + XCHG_BYTES + 16; // 1 KB slack to align the stage
+        static_assert((C::N & (C::N - 1)) == 0 && C::N >= 32, "power-of-two lengths only");
+        __device__ static __forceinline__ int prow(int e)
+        {
+            return e + (e >> 5);
+        }
+    };
+
+    template <class C, int P>
+    __device__ __forceinline__ void colstream_compute(typename ColStream<C>::C2 (&r)[ColStream<C>::EPT],
+                                                      const typename C::T2* __restrict__ tw,
+                                                      const int tl)
+    {
+        using CC = ColStream<C>;
+        using PP = ColWidePass<C, P>;
+        static_assert(PP::FULL && PP::BPT * PP::W == CC::EPT, "every radix must divide the points per thread");
+#pragma unroll
+        for(int i = 0; i < PP::BPT; ++i)
+        {
+            if constexpr(P > 0)
+            {
+                const int k = (tl + i * C::TPT) % PP::CH;
+#pragma unroll
+                for(int j = 1; j < PP::W; ++j)
+                    r[i * PP::W + j] = CC::SV::twmul(r[i * PP::W + j], tw[PP::TWO + (j - 1) * PP::CH + k]);
+            }
+            Butterfly<PP::W, typename CC::C2>::run(*reinterpret_cast<typename CC::C2(*)[PP::W]>(&r[i * PP::W]));
+        }
+    }
+
+    // exchange after pass P: results of pass P (in r) -> inputs of pass P+1 (in r), one component at a time
+    template <class C, int P>
+    __device__ __forceinline__ void colstream_exchange(typename ColStream<C>::C2 (&r)[ColStream<C>::EPT],
+                                                       typename ColStream<C>::P* xs,
+                                                       const int                 tl,
+                                                       const int                 u,
+                                                       const bool                first_of_tile)
+    {
+        using CC = ColStream<C>;
+        using PP = ColWidePass<C, P>;
+        using PN = ColWidePass<C, P + 1>;
+#pragma unroll
+        for(int half = 0; half < 2; ++half)
+        {
+            // the buffer must be free: its previous readers are past a barrier (the stage barrier
+            // covers the first use in a tile)
+            if(!(first_of_tile && half == 0))
+                __syncthreads();
+#pragma unroll
+            for(int i = 0; i < PP::BPT; ++i)
+            {
+                const int b  = tl + i * C::TPT;
+                const int k  = b % PP::CH;
+                const int e0 = (b / PP::CH) * (PP::W * PP::CH) + k;
+#pragma unroll
+                for(int j = 0; j < PP::W; ++j)
+                    xs[CC::prow(e0 + j * PP::CH) * CC::UNITS + u] = half == 0 ? r[i * PP::W + j].x : r[i * PP::W + j].y;
+            }
+            __syncthreads();
+#pragma unroll
+            for(int i = 0; i < PN::BPT; ++i)
+            {
+                const int b = tl + i * C::TPT;
+#pragma unroll
+                for(int j = 0; j < PN::W; ++j)
+                {
+                    const typename CC::P v = xs[CC::prow(b + j * PN::NB) * CC::UNITS + u];
+                    if(half == 0)
+                        r[i * PN::W + j].x = v;
+                    else
+                        r[i * PN::W + j].y = v;
+                }
+            }
+        }
+    }
+
+    template <class C, int P, bool BLK>
+    __device__ __forceinline__ void colstream_from(typename ColStream<C>::C2 (&r)[ColStream<C>::EPT],
+                                                   typename ColStream<C>::P* xs,
+                                                   const typename C::T2* __restrict__ tw,
+                                                   const int            tl,
+                                                   const int            u,
+                                                   const b200fft_kargs& a,
+                                                   typename C::T2*      gout,
+                                                   const long long      obase,
+                                                   const typename C::T  sx,
+                                                   const typename C::T  sy)
+    {
+        using CC = ColStream<C>;
+        using PP = ColWidePass<C, P>;
+        using T2 = typename C::T2;
+        using U  = typename CC::U;
+        colstream_compute<C, P>(r, tw, tl);
+        if constexpr(P == C::NPASS - 1)
+        {
+#pragma unroll
+            for(int i = 0; i < PP::BPT; ++i)
+            {
+                const int b   = tl + i * C::TPT;
+                const int k   = b % PP::CH;
+                const int e0  = (b / PP::CH) * (PP::W * PP::CH) + k;
+                T2*       q   = gout + (long long)e0 * a.out.es;
+                const long long ost = (long long)PP::CH * a.out.es;
+#pragma unroll
+                for(int j = 0; j < PP::W; ++j)
+                {
+                    T2* dst = BLK ? blk_address<T2>(a.out, obase, e0 + j * PP::CH) : q + j * ost;
+                    *reinterpret_cast<U*>(dst) = CC::SV::pack(r[i * PP::W + j], sx, sy);
+                }
+            }
+        }
+        else
+        {
+            colstream_exchange<C, P>(r, xs, tl, u, P == 0);
+            colstream_from<C, P + 1, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+        }
+    }
+
+    // kargs as for the other column kernels; aux[3] = device error flag (int*).  `map` describes
+    // the input array: dimension 0 = 8-byte elements along the columns, 1 = the transform,
+    // 2 / 3 = the outer dimensions on[1] / on[2].
+    template <class C, bool BLK>
+    __global__ void __launch_bounds__(ColStream<C>::THREADS, C::MINB)
+        stockham_colstream_kernel(const __grid_constant__ b200fft_kargs a, const __grid_constant__ CUtensorMap map)
+    {
+        using CC = ColStream<C>;
+        using T  = typename C::T;
+        using T2 = typename C::T2;
+        using U  = typename CC::U;
+        using C2 = typename CC::C2;
+        extern __shared__ unsigned char smem_dyn[];
+        // the stage is the destination of tensor copies: 128-byte alignment (1 KB to be safe)
+        unsigned char* smem_raw
+            = smem_dyn + ((1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u);
+        U*                 stage = reinterpret_cast<U*>(smem_raw);
+        typename CC::P*    xs    = reinterpret_cast<typename CC::P*>(smem_raw + CC::STAGE_BYTES);
+        uint64_t*          full  = reinterpret_cast<uint64_t*>(smem_raw + CC::STAGE_BYTES + CC::XCHG_BYTES);
+
+        const int tid = threadIdx.x;
+        const int u   = tid % CC::UNITS;
+        const int tl  = tid / CC::UNITS;
+        const T2* __restrict__ tw = reinterpret_cast<const T2*>(a.twiddles);
+        const T sgn = a.inverse ? (T)-1 : (T)1;
+        const T sx  = a.use_scale ? (T)a.scale : (T)1;
+        const T sy  = sx * sgn;
+        int*    err = reinterpret_cast<int*>(const_cast<void*>(a.aux[3]));
+
+        const unsigned long long ntiles = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];
+        const unsigned long long first  = blockIdx.x;
+        const unsigned long long stride = gridDim.x;
+
+        if(tid == 0)
+        {
+            ptx::mbar_init(full, 1);
+            ptx::fence_mbar_init();
+        }
+        __syncthreads();
+
+        // thread 0 only: the boxes of one tile.  The tensor map lists its dimensions 1..3 by ascending
+        // stride; iaux[3] tells where the transform (bits 0-1), outer 1 (2-3) and outer 2 (4-5) ended up.
+        const int pe = (int)(a.iaux[3] & 3), p1 = (int)((a.iaux[3] >> 2) & 3), p2 = (int)((a.iaux[3] >> 4) & 3);
+        auto issue_load = [&](unsigned long long tile) {
+            const TilePos tp = decode_tile(a, (unsigned)tile, CC::COLS);
+            ptx::mbar_expect_tx(full, CC::STAGE_BYTES + B200FFT_TEST_EXTRA_TX);
+#pragma unroll
+            for(int bx = 0; bx < CC::NBOX; ++bx)
+            {
+                const int row = bx * CC::BOX_ROWS;
+                const int c1  = pe == 0 ? row : (p1 == 0 ? (int)tp.i1 : (int)tp.i2);
+                const int c2  = pe == 1 ? row : (p1 == 1 ? (int)tp.i1 : (int)tp.i2);
+                const int c3  = pe == 2 ? row : (p1 == 2 ? (int)tp.i1 : (int)tp.i2);
+                ptx::tma_load_4d(reinterpret_cast<unsigned char*>(stage) + (size_t)bx * CC::BOX_ROWS * 128,
+                                 &map,
+                                 (int)(tp.i0_first * (unsigned)(sizeof(T2) / 8)),
+                                 c1,
+                                 c2,
+                                 c3,
+                                 full);
+            }
+        };
+        if(tid == 0 && first < ntiles)
+            issue_load(first);
+
+        unsigned phase = 0;
+        for(unsigned long long tile = first; tile < ntiles; tile += stride)
+        {
+            const bool landed = ptx::mbar_wait(full, phase);
+            phase ^= 1u;
+            C2 r[CC::EPT];
+            if(landed)
+            {
+                // pass-0 inputs: butterfly tl reads rows tl + j * NB0
+                using P0 = ColWidePass<C, 0>;
+                static_assert(P0::BPT * P0::W == CC::EPT && P0::FULL, "pass 0 must cover the points of a thread");
+#pragma unroll
+                for(int i = 0; i < P0::BPT; ++i)
+#pragma unroll
+                    for(int j = 0; j < P0::W; ++j)
+                        r[i * P0::W + j] = CC::SV::unpack(stage[(tl + i * C::TPT + j * P0::NB) * CC::UNITS + u], sgn);
+            }
+            // the stage is free once every thread has taken its points; a wait that gave up is
+            // learnt by the whole CTA here
+            if(__syncthreads_or(landed ? 0 : 1))
+            {
+                if(tid == 0)
+                {
+                    if(err)
+                        atomicExch(err, 1);
+                    ptx::mbar_wait(full, phase ^ 1u); // the copy may still be in flight: give it one more bounded wait
+                }
+                __syncthreads();
+                return;
+            }
+            const unsigned long long next = tile + stride;
+            if(tid == 0 && next < ntiles)
+                issue_load(next);
+
+            const TilePos   tp    = decode_tile(a, (unsigned)tile, CC::COLS);
+            const long long obase = view_base(a.out, tp.i0_first + u * CC::VEC, tp.i1, tp.i2);
+            T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
+            colstream_from<C, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+        }
+    }
+
+    // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the library does not link libcuda)
+    typedef CUresult (*tmap_encode_fn)(CUtensorMap*,
+                                       CUtensorMapDataType,
+                                       cuuint32_t,
+                                       void*,
+                                       const cuuint64_t*,
+                                       const cuuint64_t*,
+                                       const cuuint32_t*,
+                                       const cuuint32_t*,
+                                       CUtensorMapInterleave,
+                                       CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion,
+                                       CUtensorMapFloatOOBfill);
+    inline tmap_encode_fn tmap_encoder()
+    {
+        static tmap_encode_fn  fn = nullptr;
+        static std::once_flag once;
+        std::call_once(once, [] {
+            void*                           p = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess
+               && q == cudaDriverEntryPointSuccess)
+                fn = reinterpret_cast<tmap_encode_fn>(p);
+        });
+        return fn;
+    }
+
+    template <class C, bool BLK>
+    cudaError_t launch_colstream_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
+    {
+        using CC                      = ColStream<C>;
+        using T2                      = typename C::T2;
+        static int        blocks_per_sm[64] = {};
+        static int        sm_count[64]      = {};
+        static std::mutex mtx;
+        int               dev = 0;
+        cudaGetDevice(&dev);
+        if(dev < 0 || dev >= 64)
+            return cudaErrorInvalidDevice;
+        auto kern = stockham_colstream_kernel<C, BLK>;
+        {
+            std::lock_guard<std::mutex> g(mtx);
+            if(!blocks_per_sm[dev])
+            {
+                cudaError_t e
+                    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CC::SMEM_BYTES);
+                if(e != cudaSuccess)
+                    return e;
+                int nb = 0;
+                e      = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, CC::THREADS, CC::SMEM_BYTES);
+                if(e != cudaSuccess)
+                    return e;
+                cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+                blocks_per_sm[dev] = nb > 0 ? nb : 1;
+            }
+        }
+        if(ntiles == 0)
+            return cudaSuccess;
+        if(ntiles > 0x7fffffffull)
+            return cudaErrorInvalidConfiguration;
+        tmap_encode_fn enc = tmap_encoder();
+        if(!enc)
+            return cudaErrorNotSupported;
+        // The input array as a 4D tensor of 8-byte elements: dimension 0 runs along the columns; the
+        // transform dimension and the two outer dimensions follow by ascending stride (unit-length
+        // dimensions last, with a stride that continues the sequence).
+        if(a.in.es <= 0 || (a.on[1] > 1 && a.in.os[1] <= 0) || (a.on[2] > 1 && a.in.os[2] <= 0))
+            return cudaErrorInvalidValue;
+        struct Dim
+        {
+            cuuint64_t len, stride;
+            int        which; // 0 transform, 1 outer 1, 2 outer 2
+        };
+        Dim d[3] = {{(cuuint64_t)C::N, (cuuint64_t)a.in.es * sizeof(T2), 0},
+                    {a.on[1], (cuuint64_t)a.in.os[1] * sizeof(T2), 1},
+                    {a.on[2], (cuuint64_t)a.in.os[2] * sizeof(T2), 2}};
+        auto before = [](const Dim& x, const Dim& y) {
+            const bool ux = x.len <= 1 && x.which != 0, uy = y.len <= 1 && y.which != 0;
+            if(ux != uy)
+                return uy; // real dimensions first
+            return x.stride < y.stride;
+        };
+        for(int i = 0; i < 3; ++i)
+            for(int j = i + 1; j < 3; ++j)
+                if(before(d[j], d[i]))
+                    std::swap(d[i], d[j]);
+        for(int i = 1; i < 3; ++i)
+            if(d[i].len <= 1 && d[i].which != 0)
+            {
+                d[i].len    = 1;
+                d[i].stride = d[i - 1].stride * d[i - 1].len;
+            }
+        const cuuint64_t ce         = sizeof(T2) / 8;
+        const cuuint64_t dims[4]    = {(cuuint64_t)a.on[0] * ce, d[0].len, d[1].len, d[2].len};
+        const cuuint64_t strides[3] = {d[0].stride, d[1].stride, d[2].stride};
+        cuuint32_t       box[4]     = {16, 1, 1, 1};
+        long long        perm       = 0;
+        for(int i = 0; i < 3; ++i)
+        {
+            if(d[i].which == 0)
+                box[1 + i] = (cuuint32_t)CC::BOX_ROWS;
+            perm |= (long long)i << (2 * d[i].which);
+        }
+        b200fft_kargs ka = a;
+        ka.iaux[3]       = perm;
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        alignas(64) CUtensorMap map;
+        if(enc(&map,
+               CU_TENSOR_MAP_DATA_TYPE_UINT64,
+               4,
+               a.in.p[0],
+               dims,
+               strides,
+               box,
+               estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+           != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+        unsigned long long grid = (unsigned long long)blocks_per_sm[dev] * sm_count[dev];
+        if(grid > ntiles)
+            grid = ntiles;
+        kern<<<(unsigned)grid, CC::THREADS, CC::SMEM_BYTES, stream>>>(ka, map);
+        return cudaGetLastError();
+    }
+} // namespace b200fft

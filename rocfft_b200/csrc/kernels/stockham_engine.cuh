@@ -27,6 +27,7 @@
 #pragma once
 #include "fft_types.cuh"
 #include "kargs.h"
+#include <atomic>
 #include <cuda_runtime.h>
 
 namespace b200fft
@@ -788,7 +789,7 @@ namespace b200fft
     template <class C>
     cudaError_t launch_bluestein_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
-        static bool attr_done[64] = {};
+        static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int         dev           = 0;
         cudaGetDevice(&dev);
         if(C::SMEM_BYTES > 48 * 1024 && dev < 64 && !attr_done[dev])
@@ -812,7 +813,7 @@ namespace b200fft
     template <class C>
     cudaError_t launch_tile_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
-        static bool attr_done[64] = {};
+        static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int         dev           = 0;
         cudaGetDevice(&dev);
         if(C::SMEM_BYTES > 48 * 1024 && dev < 64 && !attr_done[dev])

@@ -25,12 +25,14 @@
 // a ragged last tile whose byte count is not a multiple of 16 is moved with
 // plain loads and stores.  Base pointers must be 16-byte aligned (the launch
 // layer checks and otherwise uses the non-TMA kernel).  Every mbarrier wait is
-// bounded: on expiry the kernel raises the plan's device error flag, drains its
-// own bulk stores and returns.  No multicast, no clusters: the kernel is legal
+// bounded: on expiry the whole CTA learns of it at the next barrier, raises the
+// plan's device error flag, drains its own bulk stores, gives the loads still in
+// flight one more bounded wait and returns.  No multicast, no clusters: the kernel is legal
 // in multi-GPU runs.
 #pragma once
 #include "stockham_engine.cuh"
 #include <cstdint>
+#include <mutex>
 
 namespace b200fft
 {
@@ -43,6 +45,12 @@ namespace b200fft
 
 #ifndef B200FFT_MBAR_SPIN
 #define B200FFT_MBAR_SPIN (1u << 22) // try_wait attempts before a wait gives up
+#endif
+// Test hook: bytes added to every expected transaction count.  With a non-zero value no load
+// phase ever completes, so the bounded waits run out although every copy has landed; the
+// wait-expiry test builds a probe with this and a short B200FFT_MBAR_SPIN.  Always 0 in the library.
+#ifndef B200FFT_TEST_EXTRA_TX
+#define B200FFT_TEST_EXTRA_TX 0u
 #endif
 
     namespace ptx
@@ -190,7 +198,7 @@ namespace b200fft
             const int      s     = (int)(k % NST);
             if((bytes & 15u) == 0)
             {
-                ptx::mbar_expect_tx(&full[s], bytes);
+                ptx::mbar_expect_tx(&full[s], bytes + B200FFT_TEST_EXTRA_TX);
                 ptx::bulk_load(stages + (size_t)s * R::STAGE_ELEMS,
                                gin + (size_t)tile * C::TPB * R::IN_ROW,
                                bytes,
@@ -210,12 +218,21 @@ namespace b200fft
             const unsigned tile   = first + k * stride;
             const unsigned nvalid = tile_rows(k);
             T2*            stage  = stages + (size_t)s * R::STAGE_ELEMS;
-            if(!ptx::mbar_wait(&full[s], (k / NST) & 1u))
+            // a wait that gave up is learnt by the whole CTA at this barrier, so that it leaves in step
+            const bool landed = ptx::mbar_wait(&full[s], (k / NST) & 1u);
+            if(__syncthreads_or(landed ? 0 : 1))
             {
-                if(err)
-                    atomicExch(err, 1);
                 if(tid == 0)
-                    ptx::bulk_wait_all();
+                {
+                    if(err)
+                        atomicExch(err, 1);
+                    ptx::bulk_wait_all(); // our own stores
+                    // loads issued for later tiles may still be in flight towards this CTA's shared
+                    // memory: give each one more bounded wait before the memory is released
+                    for(unsigned kk = k; kk < k + (unsigned)NST - 1 && kk < mycount; ++kk)
+                        ptx::mbar_wait(&full[kk % NST], (kk / NST) & 1u);
+                }
+                __syncthreads();
                 return;
             }
             const unsigned in_bytes  = nvalid * (unsigned)(R::IN_ROW * sizeof(T2));
@@ -385,13 +402,15 @@ namespace b200fft
     cudaError_t launch_rows_tma_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
         using R                     = RowsTma<C, MODE, NST>;
-        static int  blocks_per_sm[64] = {};
-        static int  sm_count[64]      = {};
-        int         dev               = 0;
+        static int        blocks_per_sm[64] = {};
+        static int        sm_count[64]      = {};
+        static std::mutex mtx;
+        int               dev = 0;
         cudaGetDevice(&dev);
-        if(dev >= 64)
+        if(dev < 0 || dev >= 64)
             return cudaErrorInvalidDevice;
         auto kern = stockham_rows_tma_kernel<C, MODE, NST>;
+        std::unique_lock<std::mutex> guard(mtx);
         if(!blocks_per_sm[dev])
         {
             cudaError_t e
@@ -405,11 +424,13 @@ namespace b200fft
             cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
             blocks_per_sm[dev] = nb > 0 ? nb : 1;
         }
+        const unsigned long long resident = (unsigned long long)blocks_per_sm[dev] * sm_count[dev];
+        guard.unlock();
         if(ntiles == 0)
             return cudaSuccess;
         if(ntiles > 0x7fffffffull)
             return cudaErrorInvalidConfiguration;
-        unsigned long long grid = (unsigned long long)blocks_per_sm[dev] * sm_count[dev];
+        unsigned long long grid = resident;
         if(grid > ntiles)
             grid = ntiles;
         kern<<<(unsigned)grid, C::THREADS, R::SMEM_BYTES, stream>>>(a);

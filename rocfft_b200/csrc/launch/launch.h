@@ -39,10 +39,10 @@ typedef enum b200fft_variant
     // need even strides, an even column count and 16-byte aligned bases
     B200FFT_COL_PAIR     = 13,
     B200FFT_COL_PAIR_BLK = 14,
-    // persistent column kernels with 128-byte-wide tiles and asynchronous prefetch
-    // (stockham_colwide.cuh); column count must be a multiple of the tile width
-    B200FFT_COL_WIDE     = 15,
-    B200FFT_COL_WIDE_BLK = 16,
+    // persistent column kernels with 128-byte-wide tiles loaded by the tensor copy engine
+    // (stockham_colstream.cuh); column count must be a multiple of the tile width
+    B200FFT_COL_TMA     = 15,
+    B200FFT_COL_TMA_BLK = 16,
     // 128-byte-wide column tiles shared by a cluster of two CTAs through distributed shared
     // memory (stockham_colcluster.cuh); power-of-two lengths
     B200FFT_COL_CL     = 17,

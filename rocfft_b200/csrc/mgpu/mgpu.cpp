@@ -6,7 +6,8 @@
 // library/src/tree_node.cpp:846-901 (CommAllToAllv over MPI_Ialltoallv).
 //
 // Design (differs from the reference on purpose):
-//   * The exchange runs over NCCL grouped send/recv on NVLink, not MPI.
+//   * The exchange crosses NVLink as plain peer stores issued by the FFT kernels themselves
+//     (default), or as NCCL grouped send/recv (option); never MPI.
 //   * There are no pack or unpack kernels.  The three local FFT passes write
 //     and read the exchange buffers in packed order themselves:
 //       pass A  FFT along Y (column tiles) of the local Z-slab; its store splits Y
@@ -464,7 +465,10 @@ namespace b200fft
             cudaStreamDestroy(sp->comm_stream);
         if(sp->p2p)
         {
-            // unmap the peers' buffers, then release our own
+            // Destruction is collective: every rank first unmaps the peers' buffers, then all ranks
+            // meet in a barrier, and only then does each free the memory it exported (freeing
+            // exported memory while another process still has it mapped is undefined).
+            cudaDeviceSynchronize();
             for(int q = 0; q < (int)sp->peer_r.size(); ++q)
             {
                 if(q == sp->rank)
@@ -473,6 +477,12 @@ namespace b200fft
                     cudaIpcCloseMemHandle(sp->peer_r[q]);
                 if(sp->peer_r2[q])
                     cudaIpcCloseMemHandle(sp->peer_r2[q]);
+            }
+            if(sp->P > 1 && sp->bar && nccl().ok && !getenv("ROCFFT_B200_MGPU_LOCAL_DESTROY"))
+            {
+                cudaMemsetAsync(sp->bar + 2, 0, sizeof(int), nullptr);
+                if(nccl().AllReduce(sp->bar + 2, sp->bar + 10, 1, ncclInt, ncclSum, sp->comm, nullptr) == ncclSuccess)
+                    cudaStreamSynchronize(nullptr);
             }
             cudaFree(sp->tab_a);
             cudaFree(sp->tab_b);
@@ -522,6 +532,12 @@ namespace b200fft
             for(auto& c : *v)
                 if(c && c->dev_error)
                     out.push_back(c->dev_error);
+        // sums of the ranks' failure flags, carried by the two phase barriers
+        if(sp->p2p && sp->bar && sp->P > 1)
+        {
+            out.push_back(sp->bar + 8);
+            out.push_back(sp->bar + 9);
+        }
     }
 
     rocfft_status execute_multi_device_plan(rocfft_plan_t*                 plan,
@@ -556,22 +572,42 @@ namespace b200fft
                     cudaEventRecord(ev[i], s);
                 }
             };
+            // A rank that fails locally (bad argument, launch error) must not leave the others
+            // waiting in a barrier that it never enters: the passes are skipped from the failure
+            // on, but BOTH barriers are still enqueued, and each carries the sum of the ranks'
+            // failure flags, which lands in every rank's barrier words (bar[8], bar[9]).  Those
+            // words are part of what b200fft_plan_device_error reports, so every rank can learn
+            // that the step's result is not valid; the failing rank itself returns the failure.
+            rocfft_status st = rocfft_status_success;
+            if(!in || !in[0] || (plan->placement == rocfft_placement_notinplace && (!out || !out[0])))
+                st = rocfft_status_failure;
+            auto flag = [&](int slot) {
+                // barrier word of this rank: 0 while healthy, nonzero after a local failure
+                cudaMemsetAsync(sp->bar + slot, st == rocfft_status_success ? 0 : 1, sizeof(int), s);
+            };
             mark(0);
-            rocfft_status st = execute_core(*sp->passA[0], in, out, nullptr, s);
-            if(st != rocfft_status_success)
-                return st;
+            if(st == rocfft_status_success)
+                st = execute_core(*sp->passA[0], in, out, nullptr, s);
             mark(1);
-            if(sp->P > 1 && !barrier(0))
-                return rocfft_status_failure;
+            if(sp->P > 1)
+            {
+                flag(0);
+                if(!barrier(0))
+                    return rocfft_status_failure; // the communicator itself is broken: nothing more can be enqueued
+            }
             mark(2);
-            st = execute_core(*sp->passB[0], in, out, nullptr, s);
-            if(st != rocfft_status_success)
-                return st;
+            if(st == rocfft_status_success)
+                st = execute_core(*sp->passB[0], in, out, nullptr, s);
             mark(3);
-            if(sp->P > 1 && !barrier(1))
-                return rocfft_status_failure;
+            if(sp->P > 1)
+            {
+                flag(1);
+                if(!barrier(1))
+                    return rocfft_status_failure;
+            }
             mark(4);
-            st = execute_core(*sp->passC[0], in, out, nullptr, s);
+            if(st == rocfft_status_success)
+                st = execute_core(*sp->passC[0], in, out, nullptr, s);
             mark(5);
             if(timing)
             {

@@ -483,40 +483,60 @@ namespace b200fft
                 set_blk(a.out, s.out_blk, s.out_bs);
                 a.out.blk_ptrs = s.out_blk_ptrs;
                 fill_outer(o, a, st.loops);
-                // column tiles: the persistent full-line kernel when the layout allows it
+                // Column tiles with 128-byte-wide rows.  Two designs exist:
+                //  * the persistent TMA-fed kernel (stockham_colstream.cuh): tensor-copy loads of the next
+                //    tile in flight while the current one is transformed, packed fp32 arithmetic on two
+                //    columns per thread; default for 1024 points in both precisions
+                //    (ROCFFT_B200_COLTMA=1 extends it to every length it exists for,
+                //    ROCFFT_B200_NO_COLTMA forbids it);
+                //  * cluster-of-two kernels over distributed shared memory (ROCFFT_B200_COLCLUSTER forces
+                //    them, ROCFFT_B200_NO_COLCLUSTER forbids them).  Measured (fp32): the push-exchange
+                //    cluster kernel runs a 1024-point column pass at 67 % of the copy rate whatever the
+                //    row pitch, the 64-byte-tile kernels at 57-67 % for pitches up to 2 MB and 45 % from
+                //    4 MB on (every row of a tile in its own page).  512 points: the cluster kernel wins
+                //    at megabyte pitches (512^3: 1.30 vs 1.50 ms), loses at small ones; 256 points: it loses.
                 bool wide_chosen = false;
-                // Two full-line designs exist: a persistent one-CTA-per-SM kernel (ROCFFT_B200_COLWIDE,
-                // experimental) and cluster-of-two kernels over distributed shared memory
-                // (ROCFFT_B200_COLCLUSTER forces them, ROCFFT_B200_NO_COLCLUSTER forbids them).
-                // Measured (fp32): the push-exchange cluster kernel (128-byte-wide tiles) runs a 1024-point
-                // column pass at 67 % of the copy rate whatever the row pitch, the 64-byte-tile kernels at
-                // 57-67 % for pitches up to 2 MB and 45 % from 4 MB on (every row of a tile in its own page).
-                // 512 points: the cluster kernel wins at megabyte pitches (512^3: 1.30 vs 1.50 ms), loses at
-                // small ones (512 x 512 x 512 images: 0.82 vs 0.78 ms); 256 points: it loses.
                 const long long pitch_bytes = std::llabs(a.in.es) * 8;
                 const bool      prefer_cluster
                     = prec_ == 0 && s.n <= 1024 && (s.n >= 1024 || (s.n >= 512 && pitch_bytes >= (1ll << 20)));
+                const bool prefer_tma = !getenv("ROCFFT_B200_NO_COLTMA") && !getenv("ROCFFT_B200_COLCLUSTER")
+                                        && (s.n == 1024 || getenv("ROCFFT_B200_COLTMA"));
                 if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
-                   && (getenv("ROCFFT_B200_COLWIDE") || getenv("ROCFFT_B200_COLCLUSTER")
+                   && (prefer_tma || getenv("ROCFFT_B200_COLCLUSTER")
                        || ((s.out_blk_ptrs || prefer_cluster) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
                 {
-                    // stores that cross NVLink want whole 128-byte lines: the cluster kernel is the
-                    // default when the output goes to other ranks' buffers
-                    const bool use_wide = getenv("ROCFFT_B200_COLWIDE") != nullptr;
-                    const b200fft_pool_entry* wk = pool_find(
-                        s.n,
-                        prec_,
-                        kern->variant == B200FFT_COL_STR ? (use_wide ? B200FFT_COL_WIDE : B200FFT_COL_CL)
-                                                         : (use_wide ? B200FFT_COL_WIDE_BLK : B200FFT_COL_CL_BLK));
-                    const long long al = prec_ == 0 ? 2 : 1; // strides must be multiples of 16 bytes
-                    bool ok = wk && st.loops.empty() && (a.on[0] % wk->tpb == 0) && (a.in.es % al == 0)
-                              && (a.out.es % al == 0) && (a.out.bs % al == 0) && a.in.os[0] == 1 && a.out.os[0] == 1
-                              && (s.in.byte_off[0] % 16 == 0) && (s.out.byte_off[0] % 16 == 0);
-                    for(int k = 1; k < 3; ++k)
-                        ok = ok && (a.in.os[k] % al == 0) && (a.out.os[k] % al == 0);
-                    ok = ok && (long long)s.n * std::llabs(a.in.es) < (1ll << 31)
-                         && (long long)s.n * std::llabs(a.out.es) < (1ll << 31);
-                    if(ok)
+                    const bool                plain = kern->variant == B200FFT_COL_STR;
+                    const long long           al    = prec_ == 0 ? 2 : 1; // strides must be multiples of 16 bytes
+                    const b200fft_pool_entry* wk    = nullptr;
+                    auto layout_ok = [&](const b200fft_pool_entry* k) {
+                        bool ok = k && st.loops.empty() && (a.on[0] % k->tpb == 0) && (a.in.es % al == 0)
+                                  && (a.out.es % al == 0) && (a.out.bs % al == 0) && a.in.os[0] == 1 && a.out.os[0] == 1
+                                  && (s.in.byte_off[0] % 16 == 0) && (s.out.byte_off[0] % 16 == 0);
+                        for(int k2 = 1; k2 < 3; ++k2)
+                            ok = ok && (a.in.os[k2] % al == 0) && (a.out.os[k2] % al == 0);
+                        return ok;
+                    };
+                    if(prefer_tma)
+                    {
+                        // the tensor map wants positive strides below 2^40 bytes
+                        const b200fft_pool_entry* tk = pool_find(s.n, prec_, plain ? B200FFT_COL_TMA : B200FFT_COL_TMA_BLK);
+                        bool ok = layout_ok(tk) && a.in.es > 0 && (unsigned long long)a.in.es * csize_ < (1ull << 40);
+                        for(int k2 = 1; k2 < 3; ++k2)
+                            ok = ok && (a.on[k2] <= 1 || (a.in.os[k2] > 0 && (unsigned long long)a.in.os[k2] * csize_ < (1ull << 40)));
+                        if(ok)
+                            wk = tk;
+                    }
+                    if(!wk && (getenv("ROCFFT_B200_COLCLUSTER") || ((s.out_blk_ptrs || prefer_cluster) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
+                    {
+                        // stores that cross NVLink want whole 128-byte lines: a full-line kernel is the
+                        // default when the output goes to other ranks' buffers
+                        const b200fft_pool_entry* ck = pool_find(s.n, prec_, plain ? B200FFT_COL_CL : B200FFT_COL_CL_BLK);
+                        bool ok = layout_ok(ck) && (long long)s.n * std::llabs(a.in.es) < (1ll << 31)
+                                  && (long long)s.n * std::llabs(a.out.es) < (1ll << 31);
+                        if(ok)
+                            wk = ck;
+                    }
+                    if(wk)
                     {
                         st.kern_unaligned   = kern;
                         st.ntile0_unaligned = (a.on[0] + kern->tpb - 1) / kern->tpb;
