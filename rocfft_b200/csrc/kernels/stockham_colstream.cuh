@@ -112,22 +112,26 @@ namespace b200fft
         }
     };
 
-    template <class C>
+    // UN = 16-byte units per tile row: 8 (128-byte rows, the width strided HBM traffic wants) or 4
+    // (64-byte rows: half the shared memory, for tiles that come out of L2)
+    template <class C, int UN = 8>
     struct ColStream
     {
+        using Cfg                        = C;
         using T                          = typename C::T;
         using SV                         = StreamVal<T>;
         using P                          = typename SV::P;
         using C2                         = typename SV::C2;
         using U                          = typename SV::U;
         static constexpr int VEC         = SV::VEC;
-        static constexpr int UNITS       = 8; // 16-byte units per 128-byte row segment
+        static constexpr int UNITS       = UN; // 16-byte units per row segment
         static constexpr int COLS        = UNITS * VEC;
         static constexpr int THREADS     = C::TPT * UNITS;
         static constexpr int EPT         = C::N / C::TPT;
         static constexpr int BOX_ROWS    = C::N < 256 ? C::N : 256;
         static constexpr int NBOX        = C::N / BOX_ROWS;
-        static constexpr unsigned STAGE_BYTES = (unsigned)C::N * 128u;
+        static constexpr unsigned ROW_BYTES   = (unsigned)UN * 16u;
+        static constexpr unsigned STAGE_BYTES = (unsigned)C::N * ROW_BYTES;
         static constexpr int      XROWS       = C::N + (C::N >> 5) + 1; // one pad row per 32 keeps both passes conflict-free
         static constexpr size_t   XCHG_BYTES  = C::NPASS > 1 ? (size_t)XROWS * UNITS * 8 : 0;
         static constexpr size_t   SMEM_BYTES  = 1024 + STAGE_BYTES + XCHG_BYTES + 16; // 1 KB slack to align the stage
@@ -138,12 +142,12 @@ namespace b200fft
         }
     };
 
-    template <class C, int P>
-    __device__ __forceinline__ void colstream_compute(typename ColStream<C>::C2 (&r)[ColStream<C>::EPT],
-                                                      const typename C::T2* __restrict__ tw,
+    template <class CC, int P>
+    __device__ __forceinline__ void colstream_compute(typename CC::C2 (&r)[CC::EPT],
+                                                      const typename CC::Cfg::T2* __restrict__ tw,
                                                       const int tl)
     {
-        using CC = ColStream<C>;
+        using C  = typename CC::Cfg;
         using PP = ColWidePass<C, P>;
         static_assert(PP::FULL && PP::BPT * PP::W == CC::EPT, "every radix must divide the points per thread");
 #pragma unroll
@@ -161,14 +165,14 @@ namespace b200fft
     }
 
     // exchange after pass P: results of pass P (in r) -> inputs of pass P+1 (in r), one component at a time
-    template <class C, int P>
-    __device__ __forceinline__ void colstream_exchange(typename ColStream<C>::C2 (&r)[ColStream<C>::EPT],
-                                                       typename ColStream<C>::P* xs,
-                                                       const int                 tl,
-                                                       const int                 u,
-                                                       const bool                first_of_tile)
+    template <class CC, int P>
+    __device__ __forceinline__ void colstream_exchange(typename CC::C2 (&r)[CC::EPT],
+                                                       typename CC::P* xs,
+                                                       const int       tl,
+                                                       const int       u,
+                                                       const bool      first_of_tile)
     {
-        using CC = ColStream<C>;
+        using C  = typename CC::Cfg;
         using PP = ColWidePass<C, P>;
         using PN = ColWidePass<C, P + 1>;
 #pragma unroll
@@ -206,23 +210,23 @@ namespace b200fft
         }
     }
 
-    template <class C, int P, bool BLK>
-    __device__ __forceinline__ void colstream_from(typename ColStream<C>::C2 (&r)[ColStream<C>::EPT],
-                                                   typename ColStream<C>::P* xs,
-                                                   const typename C::T2* __restrict__ tw,
-                                                   const int            tl,
-                                                   const int            u,
-                                                   const b200fft_kargs& a,
-                                                   typename C::T2*      gout,
-                                                   const long long      obase,
-                                                   const typename C::T  sx,
-                                                   const typename C::T  sy)
+    template <class CC, int P, bool BLK>
+    __device__ __forceinline__ void colstream_from(typename CC::C2 (&r)[CC::EPT],
+                                                   typename CC::P* xs,
+                                                   const typename CC::Cfg::T2* __restrict__ tw,
+                                                   const int                 tl,
+                                                   const int                 u,
+                                                   const b200fft_kargs&      a,
+                                                   typename CC::Cfg::T2*     gout,
+                                                   const long long           obase,
+                                                   const typename CC::T      sx,
+                                                   const typename CC::T      sy)
     {
-        using CC = ColStream<C>;
+        using C  = typename CC::Cfg;
         using PP = ColWidePass<C, P>;
         using T2 = typename C::T2;
         using U  = typename CC::U;
-        colstream_compute<C, P>(r, tw, tl);
+        colstream_compute<CC, P>(r, tw, tl);
         if constexpr(P == C::NPASS - 1)
         {
 #pragma unroll
@@ -243,8 +247,8 @@ namespace b200fft
         }
         else
         {
-            colstream_exchange<C, P>(r, xs, tl, u, P == 0);
-            colstream_from<C, P + 1, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+            colstream_exchange<CC, P>(r, xs, tl, u, P == 0);
+            colstream_from<CC, P + 1, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
         }
     }
 
@@ -301,7 +305,7 @@ namespace b200fft
                 const int c1  = pe == 0 ? row : (p1 == 0 ? (int)tp.i1 : (int)tp.i2);
                 const int c2  = pe == 1 ? row : (p1 == 1 ? (int)tp.i1 : (int)tp.i2);
                 const int c3  = pe == 2 ? row : (p1 == 2 ? (int)tp.i1 : (int)tp.i2);
-                ptx::tma_load_4d(reinterpret_cast<unsigned char*>(stage) + (size_t)bx * CC::BOX_ROWS * 128,
+                ptx::tma_load_4d(reinterpret_cast<unsigned char*>(stage) + (size_t)bx * CC::BOX_ROWS * CC::ROW_BYTES,
                                  &map,
                                  (int)(tp.i0_first * (unsigned)(sizeof(T2) / 8)),
                                  c1,
@@ -350,7 +354,7 @@ namespace b200fft
             const TilePos   tp    = decode_tile(a, (unsigned)tile, CC::COLS);
             const long long obase = view_base(a.out, tp.i0_first + u * CC::VEC, tp.i1, tp.i2);
             T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
-            colstream_from<C, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+            colstream_from<CC, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
         }
     }
 
