@@ -129,11 +129,16 @@ namespace
         std::vector<int> f;
         int              tpt, tpb, minb;
         int              r2c_tma_tpb, r2c_tma_minb; // fused real forward TMA kernel (0 = rule)
+        // packed row-pair TMA kernels (0 = rule): factor order, threads per pair, pairs per tile, resident blocks
+        std::vector<int> pk_f;
+        int              pk_tpt, pk_pairs, pk_minb;
     };
     const std::vector<Tuned> kTuned = {
         // 500 (the 1000-point real transform): measured r2c 0.160 ms with 2-row tiles x 6 CTAs/SM against
         // 0.175 ms with 4-row tiles x 3; c2r and c2c are indifferent
-        {500, 0, {20, 25}, 25, 8, 4, 2, 6},
+        // packed pairs, measured (65536 rows): 10.10.5 with 50 threads per pair, one pair per CTA, six CTAs
+        // per SM: r2c 0.150 ms, c2r 0.150 ms (scalar 20.25 kernels: 0.161 / 0.158 ms; packed 20.25: 0.170-0.181 ms)
+        {500, 0, {20, 25}, 25, 8, 4, 2, 6, {10, 10, 5}, 50, 1, 6},
     };
     const Tuned* tuned_for(int n, int prec)
     {
@@ -181,6 +186,11 @@ namespace
         // odd-length real transforms as one full-length complex kernel
         {"row_r2c_full", 20, false, "IO_REAL_IN", "IO_HERM_OUT", "COOP_NONE", "COOP_NONE"},
         {"row_c2r_full", 21, false, "IO_HERM_IN", "IO_REAL_OUT", "COOP_NONE", "COOP_NONE"},
+        // (22: whole image batches through L2, separate table)
+        // persistent TMA row kernels on PAIRS of rows in packed single precision (stockham_rows_tma.cuh)
+        {"row_tma_pk", 23, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        {"row_r2c_tma_pk", 24, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
+        {"row_c2r_tma_pk", 25, false, "IO_UNIT", "IO_UNIT", "COOP_NONE", "COOP_NONE"},
     };
     const int kTmaStages = 3;
     // padded lengths M with a single-kernel Bluestein: 2^k, 3*2^k, 5*2^k
@@ -206,6 +216,7 @@ namespace
         size_t           smem;
         std::string      cfg; // the KCfg<...> type
         bool             push = false; // cluster variants: push-exchange kernel
+        bool             pairs = false; // packed row pairs: a tile holds 2 * tpb rows
     };
 
     size_t smem_bytes(int n, int tpb, bool col, int prec, bool coop, int npass)
@@ -316,6 +327,11 @@ int main(int argc, char** argv)
                 const bool push = clv && prec == 0 && pow2 && n >= 64 && n <= 1024;
                 int        kt   = tpt; // threads per transform and factors of this kernel
                 std::vector<int> kf = ch.f;
+                if(v.id >= 23 && v.id <= 25 && tuned && tuned->pk_tpt > 0)
+                {
+                    kf = tuned->pk_f;
+                    kt = tuned->pk_tpt;
+                }
                 if(push || streamv)
                 {
                     int w0 = 8;
@@ -337,7 +353,12 @@ int main(int argc, char** argv)
                     if(!all_divide)
                         continue;
                 }
-                const bool tma = v.id >= 10 && v.id <= 12;
+                // packed row pairs: single precision, lengths whose kernels are bound by instruction issue
+                // rather than by memory (anything but powers of two), of moderate size
+                const bool pkv = v.id >= 23 && v.id <= 25;
+                if(pkv && (prec != 0 || pow2 || n < 50 || n > 2048))
+                    continue;
+                const bool tma = (v.id >= 10 && v.id <= 12) || pkv;
                 if(tma && (ch.f.size() < 2 || n < 16))
                     continue;
                 const int  esz     = prec == 0 ? 8 : 16;
@@ -368,11 +389,33 @@ int main(int argc, char** argv)
                     if(coop && !realv && tpb * esz < 32)
                         continue;
                 }
-                const bool tma_variant = v.id >= 10 && v.id <= 12;
+                const bool tma_variant = (v.id >= 10 && v.id <= 12) || pkv;
                 if(tuned && !v.col && !(coop && !realv) && !tma_variant)
                     tpb = tuned->tpb;
                 size_t sm = smem_bytes(n, tpb, v.col, prec, coop, npass);
-                if(tma)
+                if(pkv)
+                {
+                    // tpb counts row PAIRS here; a tile of 2 * tpb rows is always a multiple of 16 bytes.
+                    // Aim at ~64-128 threads and three resident CTAs: stages hold the raw rows, the work
+                    // tile 16 bytes per point of a pair.
+                    const int in_row  = v.id == 25 ? n + 1 : n;
+                    const int out_row = v.id == 24 ? n + 1 : n;
+                    const int rowmax  = std::max(in_row, out_row);
+                    auto pk_smem = [&](int pairs) {
+                        const size_t stage = (((size_t)2 * pairs * rowmax * 8 + 15) / 16) * 16;
+                        const size_t work  = (size_t)16 * (((n + (n >> 3)) | 1)) * pairs;
+                        return kTmaStages * stage + work + 8 * kTmaStages;
+                    };
+                    tpb = std::max(1, std::min(8, 128 / kt));
+                    while(tpb > 1 && 3 * (pk_smem(tpb) + 1024) > 226 * 1024)
+                        --tpb;
+                    if(tuned && tuned->pk_pairs > 0)
+                        tpb = tuned->pk_pairs;
+                    if(2 * (pk_smem(tpb) + 1024) > 226 * 1024 || kt * tpb > 512)
+                        continue;
+                    sm = pk_smem(tpb);
+                }
+                else if(tma)
                 {
                     // rows travel as one contiguous byte range per tile: both the input and
                     // the output tile must be a multiple of 16 bytes
@@ -415,12 +458,12 @@ int main(int argc, char** argv)
                 {
                     // stage (n rows x 128 bytes) + half-tile exchange buffer + alignment slack
                     tpb = 128 / esz;
-                    sm  = 1024 + (size_t)n * 128 + (size_t)(n + (n >> 5) + 1) * 64 + 16;
+                    sm  = 256 + (size_t)n * 128 + (size_t)(n + (n >> 5) + 1) * 64 + 16 + (size_t)(kf[1] - 1) * kf[0] * 16;
                 }
                 else if(sm > smem_cap)
                     continue;
-                const int threads = clv ? kt * 4 : streamv ? kt * 8 : pairv ? tpt * tpb / 2 : tpt * tpb;
-                int       minb    = std::max(1, 65536 / (threads * (push ? 170 : streamv ? 255 : (pairv || clv) ? 128 : regcap)));
+                const int threads = clv ? kt * 4 : streamv ? kt * 8 : pairv ? tpt * tpb / 2 : pkv ? kt * tpb : tpt * tpb;
+                int       minb    = std::max(1, 65536 / (threads * (push ? 170 : (streamv || pkv) ? 255 : (pairv || clv) ? 128 : regcap)));
                 if(push)
                     minb = std::min(minb, 4);
                 if(sm)
@@ -431,6 +474,8 @@ int main(int argc, char** argv)
                     minb = tuned->minb;
                 if(tuned && v.id == 11 && tuned->r2c_tma_minb > 0)
                     minb = tuned->r2c_tma_minb;
+                if(tuned && pkv && tuned->pk_minb > 0)
+                    minb = tuned->pk_minb;
 
                 Kernel k;
                 k.n       = n;
@@ -448,7 +493,8 @@ int main(int argc, char** argv)
                 for(size_t i = 0; i < kf.size(); ++i)
                     fl += (i ? "," : "") + std::to_string(kf[i]);
                 fl += ">";
-                k.cfg = std::string("KCfg<") + tname + "," + std::to_string(n) + ","
+                k.pairs = pkv;
+                k.cfg = std::string("KCfg<") + (pkv ? "pk2" : tname) + "," + std::to_string(n) + ","
                         + std::to_string(kt) + "," + std::to_string(tpb) + ","
                         + (v.col ? "true" : "false") + "," + v.ioki + "," + v.ioko + "," + v.cin + "," + v.cout_ + ","
                         + std::to_string(minb) + "," + fl + ">";
@@ -468,6 +514,8 @@ int main(int argc, char** argv)
         int              n0, n1, prec, threads, minb;
         std::vector<int> f0, f1;
         size_t           smem;
+        int              variant = 19; // 19: one image per CTA; 22: persistent, intermediate array in L2
+        int              un      = 0; // variant 22: 16-byte units per tile row
     };
     std::vector<Kernel2D> kernels2d;
     if(!g_small)
@@ -535,6 +583,30 @@ int main(int argc, char** argv)
                     }
     }
 
+    // ---- whole image batches in one persistent kernel, intermediate array in L2 (stockham_fused2d.cuh) ----
+    // 1024 x 1024 (32 x 32 passes, one butterfly per lane) in both precisions; tile rows of 128 bytes
+    // (one CTA per SM) and of 64 bytes (two CTAs per SM)
+    for(int prec = 0; prec < 2; ++prec)
+        for(int un : {8, 4})
+        {
+            const int   n     = 1024;
+            const int   esz   = prec == 0 ? 8 : 16;
+            const char* tname = prec == 0 ? "float" : "double";
+            Kernel2D    k;
+            k.n0 = k.n1 = n;
+            k.prec      = prec;
+            k.threads   = 32 * un;
+            k.f0 = k.f1 = {32, 32};
+            k.smem      = 256 + (size_t)n * un * 16 + (size_t)(n + (n >> 5) + 1) * un * 8 + 16 + 31 * 32 * 16;
+            k.minb      = un == 8 ? 1 : 2;
+            k.variant   = 22;
+            k.un        = un;
+            k.cfg0 = std::string("KCfg<") + tname + ",1024,32," + std::to_string(un * 16 / esz)
+                     + ",true,IO_STRIDED,IO_STRIDED,COOP_NONE,COOP_NONE," + std::to_string(k.minb) + ",FactorList<32,32>>";
+            k.name = std::string("fft2d_l2_") + (prec == 0 ? "sp" : "dp") + "_1024x1024_w" + std::to_string(un * 16);
+            kernels2d.push_back(k);
+        }
+
     // ---- kernel sources, spread over nfiles translation units ----
     // order by length descending so that expensive kernels spread evenly
     std::vector<size_t> order(kernels.size());
@@ -548,7 +620,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_colstream.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_colstream.cuh\"\n#include \"stockham_fused2d.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -561,6 +633,8 @@ int main(int argc, char** argv)
             o << "launch_bluestein_kernel<" << k.cfg << ">";
         else if(k.variant >= 10 && k.variant <= 12)
             o << "launch_rows_tma_kernel<" << k.cfg << ", " << (k.variant - 10) << ", " << kTmaStages << ">";
+        else if(k.variant >= 23 && k.variant <= 25)
+            o << "launch_rows_tma_kernel<" << k.cfg << ", " << (k.variant - 23) << ", " << kTmaStages << ">";
         else if(k.variant == 13 || k.variant == 14)
             o << "launch_colpair_kernel<" << k.cfg << ", " << (k.variant == 14 ? "true" : "false") << ">";
         else if(k.variant == 15 || k.variant == 16)
@@ -578,8 +652,11 @@ int main(int argc, char** argv)
         const Kernel2D& k = kernels2d[i];
         auto&           o = files[i % nfiles];
         o << "extern \"C\" cudaError_t b200fft_launch_" << k.name
-          << "(const b200fft_kargs* a, unsigned long long nimages, cudaStream_t s)\n{\n    return launch_2d_kernel<"
-          << k.cfg0 << ", " << k.cfg1 << ", " << k.minb << ">(*a, nimages, s);\n}\n\n";
+          << "(const b200fft_kargs* a, unsigned long long nimages, cudaStream_t s)\n{\n    return ";
+        if(k.variant == 22)
+            o << "launch_fused2d_kernel<" << k.cfg0 << ", " << k.un << ">(*a, nimages, s);\n}\n\n";
+        else
+            o << "launch_2d_kernel<" << k.cfg0 << ", " << k.cfg1 << ", " << k.minb << ">(*a, nimages, s);\n}\n\n";
     }
 
     // ---- function pool ----
@@ -592,8 +669,8 @@ int main(int argc, char** argv)
         o << "\nstatic const b200fft_pool_entry kPool[] = {\n";
         for(const Kernel& k : kernels)
         {
-            o << "    {" << k.n << ", " << k.prec << ", " << k.variant << ", " << k.tpt << ", " << k.tpb
-              << ", "
+            o << "    {" << k.n << ", " << k.prec << ", " << k.variant << ", " << k.tpt << ", "
+              << (k.pairs ? 2 * k.tpb : k.tpb) << ", "
               << ((k.variant == 17 || k.variant == 18)   ? k.tpt * 4
                   : (k.variant == 15 || k.variant == 16) ? k.tpt * 8
                   : (k.variant == 13 || k.variant == 14) ? k.tpt * k.tpb / 2
@@ -612,7 +689,8 @@ int main(int argc, char** argv)
         o << "\nstatic const b200fft_pool2d_entry kPool2D[] = {\n";
         for(const Kernel2D& k : kernels2d)
         {
-            o << "    {{" << k.n0 * k.n1 << ", " << k.prec << ", 19, " << k.n0 / (k.f0[0]) << ", " << k.n1 << ", " << k.threads
+            o << "    {{" << k.n0 * k.n1 << ", " << k.prec << ", " << k.variant << ", " << k.n0 / (k.f0[0]) << ", "
+              << (k.variant == 22 ? k.un : k.n1) << ", " << k.threads
               << ", " << k.f0.size() << ", {";
             for(size_t i = 0; i < 8; ++i)
                 o << (i ? "," : "") << (i < k.f0.size() ? k.f0[i] : 0);

@@ -132,11 +132,51 @@ namespace b200fft
     {
         return pk2(__ffma2_rn(a.v, c.v, __fmul2_rn(b.v, make_float2(-s.v.x, -s.v.y))));
     }
+    __device__ __forceinline__ pk2& operator*=(pk2& a, const pk2 b)
+    {
+        a = a * b;
+        return a;
+    }
     // complex value whose parts are packed pairs: two complex numbers, structure-of-arrays
     struct pk2c
     {
         pk2 x, y;
     };
+    template <>
+    struct cx<pk2>
+    {
+        using type = pk2c;
+    };
+#endif
+
+    // type of a twiddle-table entry for values of component type T: the tables hold ordinary
+    // complex numbers also when the data are packed pairs
+    template <typename T>
+    struct twof
+    {
+        using type = typename cx<T>::type;
+    };
+    // value times table entry
+    template <typename T2>
+    B200FFT_DEVICE T2 tmul(const T2 a, const T2 w)
+    {
+        return cmul(a, w);
+    }
+#if defined(__CUDACC__)
+    template <>
+    struct twof<pk2>
+    {
+        using type = float2;
+    };
+    // both complex numbers of the pair times the same table entry
+    __device__ __forceinline__ pk2c tmul(const pk2c a, const float2 w)
+    {
+        const float2 wx = make_float2(w.x, w.x), wy = make_float2(w.y, w.y), nwy = make_float2(-w.y, -w.y);
+        pk2c         r;
+        r.x = pk2(__ffma2_rn(a.x.v, wx, __fmul2_rn(a.y.v, nwy)));
+        r.y = pk2(__ffma2_rn(a.x.v, wy, __fmul2_rn(a.y.v, wx)));
+        return r;
+    }
 #endif
 
     // forward DFT of W points held in registers, natural order in and out;

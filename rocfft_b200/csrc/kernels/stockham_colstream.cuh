@@ -90,6 +90,20 @@ namespace b200fft
             r.y = pk2(__ffma2_rn(c.x.v, wy, __fmul2_rn(c.y.v, wx)));
             return r;
         }
+        // shared-memory copy of a twiddle: both parts already broadcast to a register pair
+        using TWS = float4;
+        __device__ static __forceinline__ TWS tws(const float2 w)
+        {
+            return make_float4(w.x, w.x, w.y, w.y);
+        }
+        __device__ static __forceinline__ C2 twmul(const C2 c, const float4 w)
+        {
+            const float2 wx = make_float2(w.x, w.y), wy = make_float2(w.z, w.w), nwy = make_float2(-w.z, -w.w);
+            C2           r;
+            r.x = pk2(__ffma2_rn(c.x.v, wx, __fmul2_rn(c.y.v, nwy)));
+            r.y = pk2(__ffma2_rn(c.x.v, wy, __fmul2_rn(c.y.v, wx)));
+            return r;
+        }
     };
     template <>
     struct StreamVal<double>
@@ -109,6 +123,11 @@ namespace b200fft
         __device__ static __forceinline__ C2 twmul(const C2 c, const double2 w)
         {
             return cmul(c, w);
+        }
+        using TWS = double2;
+        __device__ static __forceinline__ TWS tws(const double2 w)
+        {
+            return w;
         }
     };
 
@@ -134,7 +153,13 @@ namespace b200fft
         static constexpr unsigned STAGE_BYTES = (unsigned)C::N * ROW_BYTES;
         static constexpr int      XROWS       = C::N + (C::N >> 5) + 1; // one pad row per 32 keeps both passes conflict-free
         static constexpr size_t   XCHG_BYTES  = C::NPASS > 1 ? (size_t)XROWS * UNITS * 8 : 0;
-        static constexpr size_t   SMEM_BYTES  = 1024 + STAGE_BYTES + XCHG_BYTES + 16; // 1 KB slack to align the stage
+        // two-pass kernels keep the twiddles of their second pass in shared memory (16 bytes per entry):
+        // the L1 cache left beside ~200 KB of shared memory is too small to hold them against the
+        // kernel's own store traffic
+        static constexpr bool     TW_SMEM     = C::NPASS == 2;
+        static constexpr int      TW_ENTRIES  = TW_SMEM ? (C::FL::get(1) - 1) * C::FL::get(0) : 0;
+        static constexpr size_t   TW_BYTES    = (size_t)TW_ENTRIES * 16;
+        static constexpr size_t   SMEM_BYTES  = 256 + STAGE_BYTES + XCHG_BYTES + 16 + TW_BYTES; // slack to align the stage to 256 bytes
         static_assert((C::N & (C::N - 1)) == 0 && C::N >= 32, "power-of-two lengths only");
         __device__ static __forceinline__ int prow(int e)
         {
@@ -142,10 +167,12 @@ namespace b200fft
         }
     };
 
-    template <class CC, int P>
-    __device__ __forceinline__ void colstream_compute(typename CC::C2 (&r)[CC::EPT],
-                                                      const typename CC::Cfg::T2* __restrict__ tw,
-                                                      const int tl)
+#ifdef B200FFT_CS_TIMING
+    __device__ long long g_cs_tm[4]; // harness only: clocks of CTA 0's thread 0 in pass 0 / exchange / pass 1 / store
+    __shared__ long long s_cs_tm[4];
+#endif
+    template <class CC, int P, class TWP>
+    __device__ __forceinline__ void colstream_compute(typename CC::C2 (&r)[CC::EPT], const TWP* __restrict__ tw, const int tl)
     {
         using C  = typename CC::Cfg;
         using PP = ColWidePass<C, P>;
@@ -158,7 +185,7 @@ namespace b200fft
                 const int k = (tl + i * C::TPT) % PP::CH;
 #pragma unroll
                 for(int j = 1; j < PP::W; ++j)
-                    r[i * PP::W + j] = CC::SV::twmul(r[i * PP::W + j], tw[PP::TWO + (j - 1) * PP::CH + k]);
+                    r[i * PP::W + j] = CC::SV::twmul(r[i * PP::W + j], tw[(CC::TW_SMEM ? 0 : PP::TWO) + (j - 1) * PP::CH + k]);
             }
             Butterfly<PP::W, typename CC::C2>::run(*reinterpret_cast<typename CC::C2(*)[PP::W]>(&r[i * PP::W]));
         }
@@ -210,10 +237,10 @@ namespace b200fft
         }
     }
 
-    template <class CC, int P, bool BLK>
+    template <class CC, int P, bool BLK, class TWP>
     __device__ __forceinline__ void colstream_from(typename CC::C2 (&r)[CC::EPT],
                                                    typename CC::P* xs,
-                                                   const typename CC::Cfg::T2* __restrict__ tw,
+                                                   const TWP* __restrict__   tw,
                                                    const int                 tl,
                                                    const int                 u,
                                                    const b200fft_kargs&      a,
@@ -226,7 +253,15 @@ namespace b200fft
         using PP = ColWidePass<C, P>;
         using T2 = typename C::T2;
         using U  = typename CC::U;
-        colstream_compute<CC, P>(r, tw, tl);
+#ifdef B200FFT_CS_TIMING
+        const long long q0 = clock64();
+#endif
+        colstream_compute<CC, P, TWP>(r, tw, tl);
+#ifdef B200FFT_CS_TIMING
+        if(threadIdx.x == 0)
+            g_cs_tm[P == 0 ? 0 : 2] += clock64() - q0;
+        const long long q1 = clock64();
+#endif
         if constexpr(P == C::NPASS - 1)
         {
 #pragma unroll
@@ -244,11 +279,19 @@ namespace b200fft
                     *reinterpret_cast<U*>(dst) = CC::SV::pack(r[i * PP::W + j], sx, sy);
                 }
             }
+#ifdef B200FFT_CS_TIMING
+            if(threadIdx.x == 0)
+                s_cs_tm[3] += clock64() - q1;
+#endif
         }
         else
         {
             colstream_exchange<CC, P>(r, xs, tl, u, P == 0);
-            colstream_from<CC, P + 1, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+#ifdef B200FFT_CS_TIMING
+            if(threadIdx.x == 0)
+                s_cs_tm[1] += clock64() - q1;
+#endif
+            colstream_from<CC, P + 1, BLK, TWP>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
         }
     }
 
@@ -265,9 +308,9 @@ namespace b200fft
         using U  = typename CC::U;
         using C2 = typename CC::C2;
         extern __shared__ unsigned char smem_dyn[];
-        // the stage is the destination of tensor copies: 128-byte alignment (1 KB to be safe)
+        // the stage is the destination of tensor copies: 128-byte alignment (256 to be safe)
         unsigned char* smem_raw
-            = smem_dyn + ((1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u);
+            = smem_dyn + ((256u - (ptx::smem_u32(smem_dyn) & 255u)) & 255u);
         U*                 stage = reinterpret_cast<U*>(smem_raw);
         typename CC::P*    xs    = reinterpret_cast<typename CC::P*>(smem_raw + CC::STAGE_BYTES);
         uint64_t*          full  = reinterpret_cast<uint64_t*>(smem_raw + CC::STAGE_BYTES + CC::XCHG_BYTES);
@@ -285,6 +328,10 @@ namespace b200fft
         const unsigned long long first  = blockIdx.x;
         const unsigned long long stride = gridDim.x;
 
+        typename CC::SV::TWS* tws = reinterpret_cast<typename CC::SV::TWS*>(smem_raw + CC::STAGE_BYTES + CC::XCHG_BYTES + 16);
+        if constexpr(CC::TW_SMEM)
+            for(int i = tid; i < CC::TW_ENTRIES; i += CC::THREADS)
+                tws[i] = CC::SV::tws(tw[C::FL::tw_offset(1) + i]);
         if(tid == 0)
         {
             ptx::mbar_init(full, 1);
@@ -318,10 +365,21 @@ namespace b200fft
             issue_load(first);
 
         unsigned phase = 0;
+#ifdef B200FFT_CS_TIMING
+        long long tm_wait = 0, tm_a = 0, tm_rest = 0, tm0 = clock64();
+        if(tid == 0)
+            s_cs_tm[0] = s_cs_tm[1] = s_cs_tm[2] = s_cs_tm[3] = 0;
+#endif
         for(unsigned long long tile = first; tile < ntiles; tile += stride)
         {
+#ifdef B200FFT_CS_TIMING
+            const long long c0 = clock64();
+#endif
             const bool landed = ptx::mbar_wait(full, phase);
             phase ^= 1u;
+#ifdef B200FFT_CS_TIMING
+            const long long c1 = clock64();
+#endif
             C2 r[CC::EPT];
             if(landed)
             {
@@ -350,12 +408,37 @@ namespace b200fft
             const unsigned long long next = tile + stride;
             if(tid == 0 && next < ntiles)
                 issue_load(next);
+#ifdef B200FFT_CS_TIMING
+            const long long c2 = clock64();
+#endif
 
             const TilePos   tp    = decode_tile(a, (unsigned)tile, CC::COLS);
             const long long obase = view_base(a.out, tp.i0_first + u * CC::VEC, tp.i1, tp.i2);
             T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
-            colstream_from<CC, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+            if constexpr(CC::TW_SMEM)
+                colstream_from<CC, 0, BLK>(r, xs, tws, tl, u, a, gout, obase, sx, sy);
+            else
+                colstream_from<CC, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+#ifdef B200FFT_CS_TIMING
+            const long long c3 = clock64();
+            tm_wait += c1 - c0;
+            tm_a += c2 - c1;
+            tm_rest += c3 - c2;
+#endif
         }
+#ifdef B200FFT_CS_TIMING
+        if(tid == 0 && a.aux[2])
+        {
+            long long* o = reinterpret_cast<long long*>(const_cast<void*>(a.aux[2])) + 4 * blockIdx.x;
+            o[0] = tm_wait;
+            o[1] = tm_a;
+            o[2] = tm_rest;
+            o[3] = clock64() - tm0;
+            if(blockIdx.x == 1)
+                for(int i = 0; i < 4; ++i)
+                    g_cs_tm[i] = s_cs_tm[i];
+        }
+#endif
     }
 
     // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the library does not link libcuda)

@@ -100,6 +100,7 @@ namespace b200fft
     {
         using T  = T_;
         using T2 = typename cx<T_>::type;
+        using TW2 = typename twof<T_>::type; // entries of the twiddle tables
         using FL = FL_;
         static constexpr int  N       = N_;
         static constexpr int  TPT     = TPT_;
@@ -291,9 +292,10 @@ namespace b200fft
     // ------------------------------------------------------------------
     template <class C, int P, class LD, class ST>
     __device__ __forceinline__ void
-        run_pass(const int t, LD ld, ST st, const typename C::T2* __restrict__ tw, const bool sync_mid)
+        run_pass(const int t, LD ld, ST st, const typename C::TW2* __restrict__ tw, const bool sync_mid)
     {
         using T2          = typename C::T2;
+        using TW2         = typename C::TW2;
         constexpr int W   = C::FL::get(P);
         constexpr int CH  = C::FL::cum(P);
         constexpr int NB  = C::N / W;
@@ -309,7 +311,7 @@ namespace b200fft
         // latency overlaps both instead of following the barrier.
         constexpr bool TW4 = (P > 0) && (C::N >= B200FFT_TW4_MIN) && (W >= 8);
         constexpr int  NA  = TW4 ? (W - 1) / 4 : 1; // legs 4, 8, ...
-        T2 wb[BPT][3], wa[BPT][NA];
+        TW2 wb[BPT][3], wa[BPT][NA];
         if constexpr(TW4)
         {
 #pragma unroll
@@ -355,22 +357,22 @@ namespace b200fft
                     {
 #pragma unroll
                         for(int b4 = 1; b4 < 4; ++b4)
-                            x[i][b4] = cmul(x[i][b4], wb[i][b4 - 1]);
+                            x[i][b4] = tmul(x[i][b4], wb[i][b4 - 1]);
 #pragma unroll
                         for(int a4 = 1; 4 * a4 < W; ++a4)
                         {
-                            x[i][4 * a4] = cmul(x[i][4 * a4], wa[i][a4 - 1]);
+                            x[i][4 * a4] = tmul(x[i][4 * a4], wa[i][a4 - 1]);
 #pragma unroll
                             for(int b4 = 1; b4 < 4; ++b4)
                                 if(4 * a4 + b4 < W)
-                                    x[i][4 * a4 + b4] = cmul(x[i][4 * a4 + b4], cmul(wa[i][a4 - 1], wb[i][b4 - 1]));
+                                    x[i][4 * a4 + b4] = tmul(x[i][4 * a4 + b4], cmul(wa[i][a4 - 1], wb[i][b4 - 1]));
                         }
                     }
                     else
                     {
 #pragma unroll
                         for(int j = 1; j < W; ++j)
-                            x[i][j] = cmul(x[i][j], tw[TWO + (j - 1) * CH + k]);
+                            x[i][j] = tmul(x[i][j], tw[TWO + (j - 1) * CH + k]);
                     }
                 }
                 Butterfly<W, T2>::run(x[i]);
@@ -390,7 +392,7 @@ namespace b200fft
     __device__ __forceinline__ void run_passes(const int                 t,
                                                const int                 c,
                                                typename C::T2*           sm,
-                                               const typename C::T2* __restrict__ tw,
+                                               const typename C::TW2* __restrict__ tw,
                                                SRC                       src,
                                                DST                       dst)
     {

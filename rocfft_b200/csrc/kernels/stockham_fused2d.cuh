@@ -57,7 +57,7 @@ namespace b200fft
 #endif
 
     template <class C, int UN>
-    struct Fused2D
+    struct FusedL2
     {
         using CC                         = ColStream<C, UN>;
         using T                          = typename C::T;
@@ -80,10 +80,10 @@ namespace b200fft
     // `map` = tensor map of the OUTPUT array (dimension 0 columns in 8-byte elements, then the
     // dimensions ordered as iaux[3] says, see stockham_colstream.cuh).
     template <class C, int UN>
-    __global__ void __launch_bounds__(Fused2D<C, UN>::THREADS, C::MINB)
+    __global__ void __launch_bounds__(FusedL2<C, UN>::THREADS, C::MINB)
         stockham_fused2d_kernel(const __grid_constant__ b200fft_kargs a, const __grid_constant__ CUtensorMap map)
     {
-        using F  = Fused2D<C, UN>;
+        using F  = FusedL2<C, UN>;
         using CC = typename F::CC;
         using T  = typename C::T;
         using T2 = typename C::T2;
@@ -93,7 +93,7 @@ namespace b200fft
         using SV = typename CC::SV;
         constexpr int N = C::N;
         extern __shared__ unsigned char smem_dyn[];
-        unsigned char* smem_raw = smem_dyn + ((1024u - (ptx::smem_u32(smem_dyn) & 1023u)) & 1023u);
+        unsigned char* smem_raw = smem_dyn + ((256u - (ptx::smem_u32(smem_dyn) & 255u)) & 255u);
         U*             stage    = reinterpret_cast<U*>(smem_raw);
         PV*            xs       = reinterpret_cast<PV*>(smem_raw + CC::STAGE_BYTES);
         uint64_t*      full     = reinterpret_cast<uint64_t*>(smem_raw + CC::STAGE_BYTES + CC::XCHG_BYTES);
@@ -112,6 +112,10 @@ namespace b200fft
         const unsigned long long nitems = (unsigned long long)(nimg + 1) * B;
         const int pe = (int)(a.iaux[3] & 3), p1 = (int)((a.iaux[3] >> 2) & 3);
 
+        // twiddles of the second pass in shared memory (both tile kinds use the same 32 x 32 table)
+        typename SV::TWS* tws = reinterpret_cast<typename SV::TWS*>(smem_raw + CC::STAGE_BYTES + CC::XCHG_BYTES + 16);
+        for(int i = tid; i < CC::TW_ENTRIES; i += F::THREADS)
+            tws[i] = SV::tws(tw[i]);
         if(tid == 0)
         {
             ptx::mbar_init(full, 1);
@@ -267,7 +271,7 @@ namespace b200fft
                 }
 #pragma unroll
                 for(int j = 1; j < 32; ++j)
-                    r[j] = SV::twmul(r[j], tw[(j - 1) * 32 + lane]);
+                    r[j] = SV::twmul(r[j], tws[(j - 1) * 32 + lane]);
                 Butterfly<32, C2>::run(r);
                 // results: points lane + 32 j of the row(s); the conjugation of an inverse transform
                 // is undone after the column pass only, the scale factor is applied there as well
@@ -298,7 +302,7 @@ namespace b200fft
                 const long long obase = (long long)img * a.out.os[1] + (long long)tile * CC::COLS + u * CC::VEC;
                 T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
                 b200fft_kargs const& ar = a;
-                colstream_from<CC, 0, false>(r, xs, tw, tl, u, ar, gout, obase, sx, sy);
+                colstream_from<CC, 0, false>(r, xs, tws, tl, u, ar, gout, obase, sx, sy);
             }
             if(s_deferred)
             {
@@ -317,7 +321,7 @@ namespace b200fft
     template <class C, int UN>
     cudaError_t launch_fused2d_kernel(const b200fft_kargs& a, unsigned long long nimages, cudaStream_t stream)
     {
-        using F  = Fused2D<C, UN>;
+        using F  = FusedL2<C, UN>;
         using CC = typename F::CC;
         using T2 = typename C::T2;
         static int        blocks_per_sm[64] = {};

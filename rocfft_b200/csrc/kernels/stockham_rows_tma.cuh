@@ -130,18 +130,77 @@ namespace b200fft
         }
     }
 
+    // Packed single precision (KCfg with T = pk2): a "transform" of the tile is a PAIR of adjacent rows
+    // whose values travel as pk2c (real parts of both rows in one register pair, imaginary parts in
+    // another): every shared-memory access of the passes moves 16 bytes for two rows and every butterfly
+    // instruction is a packed one, which halves the instruction count per point of these issue-bound
+    // kernels.  The stages hold the rows exactly as they lie in global memory (RAW = ordinary complex).
     template <class C, int MODE, int NST>
     struct RowsTma
     {
-        using T2 = typename C::T2;
+        using T2  = typename C::T2;
+        using RAW = typename C::TW2; // element type of global memory and of the stages
+        static constexpr int RPT     = sizeof(T2) / sizeof(RAW); // rows per transform slot: 2 when packed
+        static constexpr int TROWS   = C::TPB * RPT; // rows per tile
         static constexpr int IN_ROW  = (MODE == MODE_C2R) ? C::N + 1 : C::N;
         static constexpr int OUT_ROW = (MODE == MODE_R2C) ? C::N + 1 : C::N;
         static constexpr int ROWMAX  = IN_ROW > OUT_ROW ? IN_ROW : OUT_ROW;
         // stage size in elements, kept a multiple of 16 bytes
-        static constexpr int    STAGE_ELEMS = ((C::TPB * ROWMAX * (int)sizeof(T2) + 15) / 16) * 16 / (int)sizeof(T2);
-        static constexpr size_t STAGE_BYTES = (size_t)STAGE_ELEMS * sizeof(T2);
+        static constexpr int    STAGE_ELEMS = ((TROWS * ROWMAX * (int)sizeof(RAW) + 15) / 16) * 16 / (int)sizeof(RAW);
+        static constexpr size_t STAGE_BYTES = (size_t)STAGE_ELEMS * sizeof(RAW);
         static constexpr size_t WORK_BYTES  = ((sizeof(T2) * (size_t)C::SMEM_ELEMS + 15) / 16) * 16;
         static constexpr size_t SMEM_BYTES  = NST * STAGE_BYTES + WORK_BYTES + 8 * NST;
+    };
+
+    // stage <-> value conversions: one row, or two rows packed
+    template <typename T2, typename RAW>
+    struct RowIo
+    {
+        // value of slot c, point e, from rows stored with pitch `row` (rows at or beyond nvalid read as zero)
+        __device__ static __forceinline__ T2 load(const RAW* stage, int c, int e, int row, unsigned nvalid)
+        {
+            T2 v;
+            v.x = 0;
+            v.y = 0;
+            if((unsigned)c < nvalid)
+                v = stage[c * row + e];
+            return v;
+        }
+        __device__ static __forceinline__ void store(RAW* stage, int c, int e, int row, const T2 v)
+        {
+            stage[c * row + e] = v;
+        }
+        template <typename S>
+        __device__ static __forceinline__ decltype(T2::x) bcast(S s)
+        {
+            return (decltype(T2::x))s;
+        }
+    };
+    template <>
+    struct RowIo<pk2c, float2>
+    {
+        __device__ static __forceinline__ pk2c load(const float2* stage, int c, int e, int row, unsigned nvalid)
+        {
+            float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+            if((unsigned)(2 * c) < nvalid)
+                a = stage[(2 * c) * row + e];
+            if((unsigned)(2 * c + 1) < nvalid)
+                b = stage[(2 * c + 1) * row + e];
+            pk2c v;
+            v.x = pk2(a.x, b.x);
+            v.y = pk2(a.y, b.y);
+            return v;
+        }
+        __device__ static __forceinline__ void store(float2* stage, int c, int e, int row, const pk2c v)
+        {
+            stage[(2 * c) * row + e]     = make_float2(v.x.v.x, v.y.v.x);
+            stage[(2 * c + 1) * row + e] = make_float2(v.x.v.y, v.y.v.y);
+        }
+        template <typename S>
+        __device__ static __forceinline__ pk2 bcast(S s)
+        {
+            return pk2((float)s, (float)s);
+        }
     };
 
     // kargs: in.p[0] / out.p[0] 16-byte aligned bases, on[0] = number of rows,
@@ -151,13 +210,15 @@ namespace b200fft
     __global__ void __launch_bounds__(C::THREADS, C::MINB)
         stockham_rows_tma_kernel(const __grid_constant__ b200fft_kargs a)
     {
-        using T  = typename C::T;
-        using T2 = typename C::T2;
-        using R  = RowsTma<C, MODE, NST>;
+        using T   = typename C::T;
+        using T2  = typename C::T2;
+        using R   = RowsTma<C, MODE, NST>;
+        using RAW = typename R::RAW;
+        using IO  = RowIo<T2, RAW>;
         static_assert(!C::COL, "row layout only");
         static_assert(C::NPASS >= 2, "needs at least two passes");
         extern __shared__ __align__(128) unsigned char smem_raw[];
-        T2*       stages = reinterpret_cast<T2*>(smem_raw);
+        RAW*      stages = reinterpret_cast<RAW*>(smem_raw);
         T2*       sm     = reinterpret_cast<T2*>(smem_raw + NST * R::STAGE_BYTES);
         uint64_t* full   = reinterpret_cast<uint64_t*>(smem_raw + NST * R::STAGE_BYTES + R::WORK_BYTES);
 
@@ -166,14 +227,14 @@ namespace b200fft
         const int      t       = tid % C::TPT;
         const bool     inverse = (MODE == MODE_C2C) && a.inverse != 0;
         const bool     use_sc  = a.use_scale != 0;
-        const T        scale   = (T)a.scale;
+        const T        scale   = IO::bcast(a.scale);
         const unsigned nrows   = a.on[0];
         const unsigned ntiles  = a.ntile0;
-        const T2* __restrict__ tw  = reinterpret_cast<const T2*>(a.twiddles);
-        const T2* __restrict__ htw = reinterpret_cast<const T2*>(a.aux[0]);
-        int*           err         = reinterpret_cast<int*>(const_cast<void*>(a.aux[3]));
-        const T2*      gin         = reinterpret_cast<const T2*>(a.in.p[0]);
-        T2*            gout        = reinterpret_cast<T2*>(a.out.p[0]);
+        const RAW* __restrict__ tw  = reinterpret_cast<const RAW*>(a.twiddles);
+        const RAW* __restrict__ htw = reinterpret_cast<const RAW*>(a.aux[0]);
+        int*           err          = reinterpret_cast<int*>(const_cast<void*>(a.aux[3]));
+        const RAW*     gin          = reinterpret_cast<const RAW*>(a.in.p[0]);
+        RAW*           gout         = reinterpret_cast<RAW*>(a.out.p[0]);
 
         const unsigned first   = blockIdx.x;
         const unsigned stride  = gridDim.x;
@@ -189,18 +250,18 @@ namespace b200fft
 
         auto tile_rows = [&](unsigned k) -> unsigned {
             const unsigned tile = first + k * stride;
-            return min((unsigned)C::TPB, nrows - tile * (unsigned)C::TPB);
+            return min((unsigned)R::TROWS, nrows - tile * (unsigned)R::TROWS);
         };
         // thread 0 only
         auto issue_load = [&](unsigned k) {
             const unsigned tile  = first + k * stride;
-            const unsigned bytes = tile_rows(k) * (unsigned)(R::IN_ROW * sizeof(T2));
+            const unsigned bytes = tile_rows(k) * (unsigned)(R::IN_ROW * sizeof(RAW));
             const int      s     = (int)(k % NST);
             if((bytes & 15u) == 0)
             {
                 ptx::mbar_expect_tx(&full[s], bytes + B200FFT_TEST_EXTRA_TX);
                 ptx::bulk_load(stages + (size_t)s * R::STAGE_ELEMS,
-                               gin + (size_t)tile * C::TPB * R::IN_ROW,
+                               gin + (size_t)tile * R::TROWS * R::IN_ROW,
                                bytes,
                                &full[s]);
             }
@@ -216,8 +277,8 @@ namespace b200fft
         {
             const int      s      = (int)(k % NST);
             const unsigned tile   = first + k * stride;
-            const unsigned nvalid = tile_rows(k);
-            T2*            stage  = stages + (size_t)s * R::STAGE_ELEMS;
+            const unsigned nvalid = tile_rows(k); // rows
+            RAW*           stage  = stages + (size_t)s * R::STAGE_ELEMS;
             // a wait that gave up is learnt by the whole CTA at this barrier, so that it leaves in step
             const bool landed = ptx::mbar_wait(&full[s], (k / NST) & 1u);
             if(__syncthreads_or(landed ? 0 : 1))
@@ -235,16 +296,15 @@ namespace b200fft
                 __syncthreads();
                 return;
             }
-            const unsigned in_bytes  = nvalid * (unsigned)(R::IN_ROW * sizeof(T2));
-            const unsigned out_bytes = nvalid * (unsigned)(R::OUT_ROW * sizeof(T2));
+            const unsigned in_bytes  = nvalid * (unsigned)(R::IN_ROW * sizeof(RAW));
+            const unsigned out_bytes = nvalid * (unsigned)(R::OUT_ROW * sizeof(RAW));
             if(in_bytes & 15u)
             {
-                const T2* src = gin + (size_t)tile * C::TPB * R::IN_ROW;
+                const RAW* src = gin + (size_t)tile * R::TROWS * R::IN_ROW;
                 for(unsigned i = tid; i < nvalid * R::IN_ROW; i += C::THREADS)
                     stage[i] = src[i];
                 __syncthreads();
             }
-            const bool valid = (unsigned)c < nvalid;
 
             // ---------------- transform the tile ----------------
             if constexpr(MODE == MODE_C2R)
@@ -259,32 +319,28 @@ namespace b200fft
                     const int cc = idx / NP;
                     const int p  = idx % NP;
                     const int q  = H - p;
-                    T2        zp, zq;
-                    zp.x = zp.y = zq.x = zq.y = 0;
-                    if((unsigned)cc < nvalid)
+                    T2        xa = IO::load(stage, cc, p, R::IN_ROW, nvalid);
+                    T2        xb = IO::load(stage, cc, q, R::IN_ROW, nvalid);
+                    if(p == 0)
                     {
-                        T2 xa = stage[cc * R::IN_ROW + p];
-                        T2 xb = stage[cc * R::IN_ROW + q];
-                        if(p == 0)
-                        {
-                            xa.y = 0;
-                            xb.y = 0;
-                        }
-                        xb.y       = -xb.y;
-                        const T2 w = htw[p];
-                        T2       e, d, tt;
-                        e.x  = xa.x + xb.x;
-                        e.y  = xa.y + xb.y;
-                        d.x  = xa.x - xb.x;
-                        d.y  = xa.y - xb.y;
-                        tt.x = w.y;
-                        tt.y = w.x;
-                        const T2 td = cmul(tt, d);
-                        zp.x        = e.x + td.x;
-                        zp.y        = e.y + td.y;
-                        zq.x        = e.x - td.x;
-                        zq.y        = -(e.y - td.y);
+                        xa.y = IO::bcast(0);
+                        xb.y = IO::bcast(0);
                     }
+                    xb.y        = -xb.y;
+                    const RAW w = htw[p];
+                    T2        e, d, tt;
+                    e.x  = xa.x + xb.x;
+                    e.y  = xa.y + xb.y;
+                    d.x  = xa.x - xb.x;
+                    d.y  = xa.y - xb.y;
+                    tt.x = IO::bcast(w.y);
+                    tt.y = IO::bcast(w.x);
+                    const T2 td = cmul(tt, d);
+                    T2       zp, zq;
+                    zp.x = e.x + td.x;
+                    zp.y = e.y + td.y;
+                    zq.x = e.x - td.x;
+                    zq.y = -(e.y - td.y);
                     sm[C::sidx(cc, p)] = cswap(zp);
                     if(p != q && p != 0)
                         sm[C::sidx(cc, q)] = cswap(zq);
@@ -298,18 +354,14 @@ namespace b200fft
                         v.x *= scale;
                         v.y *= scale;
                     }
-                    stage[c * R::OUT_ROW + e] = v;
+                    IO::store(stage, c, e, R::OUT_ROW, v);
                 };
                 run_passes<C, 0, true, false>(t, c, sm, tw, s_src, o_dst);
             }
             else
             {
                 auto i_src = [=](int e) -> T2 {
-                    T2 v;
-                    v.x = 0;
-                    v.y = 0;
-                    if(valid)
-                        v = stage[c * R::IN_ROW + e];
+                    const T2 v = IO::load(stage, c, e, R::IN_ROW, nvalid);
                     return inverse ? cswap(v) : v;
                 };
                 if constexpr(MODE == MODE_C2C)
@@ -322,7 +374,7 @@ namespace b200fft
                             v.x *= scale;
                             v.y *= scale;
                         }
-                        stage[c * R::OUT_ROW + e] = v;
+                        IO::store(stage, c, e, R::OUT_ROW, v);
                     };
                     run_passes<C, 0, false, false>(t, c, sm, tw, i_src, o_dst);
                 }
@@ -334,7 +386,8 @@ namespace b200fft
                     constexpr int H     = C::N;
                     constexpr int NP    = H / 2 + 1;
                     constexpr int ITEMS = NP * C::TPB;
-                    const T       sc    = use_sc ? scale : (T)1;
+                    const T       sc    = use_sc ? scale : IO::bcast(1);
+                    const T       half  = IO::bcast(0.5);
                     // p = 0 needs no special case: with Z_H read as Z_0 the general formula gives
                     // X_0 = Re Z_0 + Im Z_0 and X_H = Re Z_0 - Im Z_0 with zero imaginary parts
 #pragma unroll 4
@@ -346,23 +399,23 @@ namespace b200fft
                         const T2 za = sm[C::sidx(cc, p)];
                         T2       zb = sm[C::sidx(cc, p == 0 ? 0 : q)];
                         zb.y        = -zb.y;
-                        const T2 w  = htw[p];
-                        T2       e, d, tt;
-                        e.x  = (za.x + zb.x) * (T)0.5;
-                        e.y  = (za.y + zb.y) * (T)0.5;
-                        d.x  = (za.x - zb.x) * (T)0.5;
-                        d.y  = (za.y - zb.y) * (T)0.5;
-                        tt.x = w.y;
-                        tt.y = -w.x;
+                        const RAW w = htw[p];
+                        T2        e, d, tt;
+                        e.x  = (za.x + zb.x) * half;
+                        e.y  = (za.y + zb.y) * half;
+                        d.x  = (za.x - zb.x) * half;
+                        d.y  = (za.y - zb.y) * half;
+                        tt.x = IO::bcast(w.y);
+                        tt.y = IO::bcast(-w.x);
                         const T2 td = cmul(tt, d);
                         T2       xp, xq;
                         xp.x = (e.x + td.x) * sc;
                         xp.y = (e.y + td.y) * sc;
                         xq.x = (e.x - td.x) * sc;
                         xq.y = -(e.y - td.y) * sc;
-                        stage[cc * R::OUT_ROW + p] = xp;
+                        IO::store(stage, cc, p, R::OUT_ROW, xp);
                         if(p != q)
-                            stage[cc * R::OUT_ROW + q] = xq;
+                            IO::store(stage, cc, q, R::OUT_ROW, xq);
                     }
                 }
             }
@@ -370,7 +423,7 @@ namespace b200fft
             // ---------------- hand the result to the copy engine ----------------
             ptx::fence_async_smem();
             __syncthreads();
-            T2* dst = gout + (size_t)tile * C::TPB * R::OUT_ROW;
+            RAW* dst = gout + (size_t)tile * R::TROWS * R::OUT_ROW;
             if((out_bytes & 15u) == 0)
             {
                 if(tid == 0)

@@ -240,9 +240,121 @@ namespace b200fft
         }
     }
 
+    // ------------------------------------------------------------------
+    // tiled transposing copy
+    // ------------------------------------------------------------------
+    // Role in the reference: the out-of-place tiled transpose kernel, library/src/rtc_transpose_gen.cpp:77-326
+    // (64 x 64 tiles through LDS, launch shapes library/src/rtc_transpose_kernel.cpp:40-75).  The N-D plans
+    // here need no transposes, but a layout change whose fastest dimension differs between input and output
+    // (an in-place transform with transposed output strides, for one) is a transpose all the same: the flat
+    // copy above would read lines and write single points.  This kernel moves 32 x 32 tiles through padded
+    // shared memory so that both the reads (along dimension DA, unit input stride) and the writes (along
+    // DB, unit output stride) are coalesced; the two remaining dimensions are walked by the grid.
+    // The index space has four dimensions: 0 = the points of a transform (n, es), 1..3 = on[0..2] (os[0..2]).
+    struct TransposeDims
+    {
+        unsigned  len[4];
+        long long is[4], os[4];
+        int       da, db, dc, dd;
+        unsigned  ta, tb; // tiles along DA / DB
+    };
+
+    template <typename T>
+    __global__ void __launch_bounds__(256) transpose_tile_kernel(const __grid_constant__ b200fft_eargs a,
+                                                                  const __grid_constant__ TransposeDims d)
+    {
+        using T2 = typename cx<T>::type;
+        __shared__ T2 tile[32][33];
+        unsigned long long blk = blockIdx.x;
+        const unsigned     ta  = (unsigned)(blk % d.ta);
+        blk /= d.ta;
+        const unsigned tb = (unsigned)(blk % d.tb);
+        blk /= d.tb;
+        const unsigned  ic = (unsigned)(blk % d.len[d.dc]);
+        const unsigned  id = (unsigned)(blk / d.len[d.dc]);
+        const long long ibase = (long long)ic * d.is[d.dc] + (long long)id * d.is[d.dd];
+        const long long obase = (long long)ic * d.os[d.dc] + (long long)id * d.os[d.dd];
+        const T         sc    = a.use_scale ? (T)a.scale : (T)1;
+        const T2*       in    = reinterpret_cast<const T2*>(a.in.p[0]);
+        T2*             out   = reinterpret_cast<T2*>(a.out.p[0]);
+        const unsigned  tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+        {
+            const unsigned ia = ta * 32 + tx;
+#pragma unroll
+            for(unsigned r = ty; r < 32; r += 8)
+            {
+                const unsigned ib = tb * 32 + r;
+                if(ia < d.len[d.da] && ib < d.len[d.db])
+                    tile[r][tx] = in[ibase + (long long)ia * d.is[d.da] + (long long)ib * d.is[d.db]];
+            }
+        }
+        __syncthreads();
+        {
+            const unsigned ib = tb * 32 + tx;
+#pragma unroll
+            for(unsigned r = ty; r < 32; r += 8)
+            {
+                const unsigned ia = ta * 32 + r;
+                if(ia < d.len[d.da] && ib < d.len[d.db])
+                {
+                    T2 v = tile[tx][r];
+                    v.x *= sc;
+                    v.y *= sc;
+                    out[obase + (long long)ia * d.os[d.da] + (long long)ib * d.os[d.db]] = v;
+                }
+            }
+        }
+    }
+
+    // true when the copy is a transpose this kernel serves; fills `d`
+    inline bool transpose_shape(const b200fft_eargs& a, TransposeDims& d)
+    {
+        if(a.in.planar || a.out.planar)
+            return false;
+        d.len[0] = a.n;
+        d.is[0]  = a.in.es;
+        d.os[0]  = a.out.es;
+        for(int k = 0; k < 3; ++k)
+        {
+            d.len[k + 1] = a.on[k];
+            d.is[k + 1]  = a.in.os[k];
+            d.os[k + 1]  = a.out.os[k];
+        }
+        d.da = d.db = -1;
+        for(int k = 0; k < 4; ++k)
+        {
+            if(d.len[k] < 16)
+                continue;
+            if(d.is[k] == 1 && (d.da < 0 || d.len[k] > d.len[d.da]))
+                d.da = k;
+            if(d.os[k] == 1 && (d.db < 0 || d.len[k] > d.len[d.db]))
+                d.db = k;
+        }
+        if(d.da < 0 || d.db < 0 || d.da == d.db)
+            return false; // same fastest dimension on both sides (or none): the flat copy is already coalesced
+        d.dc = d.dd = -1;
+        for(int k = 0; k < 4; ++k)
+            if(k != d.da && k != d.db)
+                (d.dc < 0 ? d.dc : d.dd) = k;
+        d.ta = (d.len[d.da] + 31) / 32;
+        d.tb = (d.len[d.db] + 31) / 32;
+        const unsigned long long blocks = (unsigned long long)d.ta * d.tb * d.len[d.dc] * d.len[d.dd];
+        return blocks > 0 && blocks <= 0x7fffffffull;
+    }
+
     template <typename T, int KIND>
     cudaError_t launch_ew(const b200fft_eargs& a, cudaStream_t stream)
     {
+        if constexpr(KIND == B200FFT_EW_COPY_C2C)
+        {
+            TransposeDims d;
+            if(a.on[0] && a.on[1] && a.on[2] && a.n && transpose_shape(a, d))
+            {
+                const unsigned long long blocks = (unsigned long long)d.ta * d.tb * d.len[d.dc] * d.len[d.dd];
+                transpose_tile_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(a, d);
+                return cudaGetLastError();
+            }
+        }
         unsigned work;
         if(KIND == B200FFT_EW_R2C_POST || KIND == B200FFT_EW_C2R_PRE)
             work = a.n / 2 + 1;

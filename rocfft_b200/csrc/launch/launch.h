@@ -52,6 +52,12 @@ typedef enum b200fft_variant
     // half out, and Hermitian half in (rebuilt by conjugate symmetry) / real rows out
     B200FFT_ROW_R2C_FULL = 20,
     B200FFT_ROW_C2R_FULL = 21,
+    // (22: B200FFT_2D_L2, separate table below)
+    // persistent TMA row kernels working on pairs of rows in packed single precision
+    // (two rows per thread slot, one packed instruction for both); tpb = rows per tile
+    B200FFT_ROW_TMA_PK     = 23,
+    B200FFT_ROW_R2C_TMA_PK = 24,
+    B200FFT_ROW_C2R_TMA_PK = 25,
 } b200fft_variant;
 
 typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);
@@ -78,6 +84,9 @@ const b200fft_pool_entry* b200fft_pool(size_t* count);
 // phase (length = n0 * n1 points per image, factors of n0); the launcher's tile count is the
 // number of images.
 #define B200FFT_2D_SINGLE 19
+// whole batches of n0 x n1 images in one persistent kernel that keeps the intermediate array in L2
+// (kernels/stockham_fused2d.cuh): same table, `base.tpb` = 16-byte units per tile row
+#define B200FFT_2D_L2 22
 typedef struct b200fft_pool2d_entry
 {
     b200fft_pool_entry base;

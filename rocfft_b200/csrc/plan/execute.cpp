@@ -56,17 +56,16 @@ namespace b200fft
 
     std::atomic<unsigned long long> g_launch_count{0};
 
-    rocfft_status execute_core(const PlanCore& core,
-                               void* const*    in,
-                               void* const*    out,
-                               void*           work,
-                               cudaStream_t    stream,
-                               cudaEvent_t*    step_events)
+    static rocfft_status run_steps(const PlanCore&          core,
+                                   const std::vector<Step>& steps,
+                                   void* const*             in,
+                                   void* const*             out,
+                                   void*                    work,
+                                   cudaStream_t             stream,
+                                   cudaEvent_t*             step_events)
     {
-        if(core.host_only)
-            return rocfft_status_failure; // no CPU fallback exists
         size_t step_index = 0;
-        for(const Step& s : core.steps)
+        for(const Step& s : steps)
         {
             if(step_events)
                 cudaEventRecord(step_events[step_index], stream);
@@ -74,6 +73,15 @@ namespace b200fft
             void *ip[2], *op[2];
             if(!resolve(s.in, in, out, work, ip) || !resolve(s.out, in, out, work, op))
                 return rocfft_status_failure;
+            if(!s.alt.empty()
+               && ((reinterpret_cast<uintptr_t>(ip[0]) | reinterpret_cast<uintptr_t>(op[0])) & 15u) != 0)
+            {
+                // misaligned bases: the ordinary passes this step stands for
+                rocfft_status st = run_steps(core, s.alt, in, out, work, stream, nullptr);
+                if(st != rocfft_status_success)
+                    return st;
+                continue;
+            }
 
             // host loops over dimensions the kernels do not index themselves
             std::vector<size_t> idx(s.loops.size(), 0);
@@ -111,7 +119,9 @@ namespace b200fft
                     if(s.kern_unaligned && misaligned)
                     {
                         a.ntile0 = s.ntile0_unaligned;
-                        e        = s.kern_unaligned->launch(&a, s.ntiles_unaligned, stream);
+                        if(s.twiddles_unaligned)
+                            a.twiddles = s.twiddles_unaligned;
+                        e = s.kern_unaligned->launch(&a, s.ntiles_unaligned, stream);
                     }
                     else
                         e = s.kern->launch(&a, s.ntiles, stream);
@@ -134,5 +144,17 @@ namespace b200fft
         if(step_events)
             cudaEventRecord(step_events[step_index], stream);
         return rocfft_status_success;
+    }
+
+    rocfft_status execute_core(const PlanCore& core,
+                               void* const*    in,
+                               void* const*    out,
+                               void*           work,
+                               cudaStream_t    stream,
+                               cudaEvent_t*    step_events)
+    {
+        if(core.host_only)
+            return rocfft_status_failure; // no CPU fallback exists
+        return run_steps(core, core.steps, in, out, work, stream, step_events);
     }
 }

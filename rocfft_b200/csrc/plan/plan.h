@@ -107,6 +107,7 @@ namespace b200fft
         const b200fft_pool_entry* kern_unaligned = nullptr;
         unsigned                  ntile0_unaligned = 0;
         unsigned long long        ntiles_unaligned = 0;
+        const void*               twiddles_unaligned = nullptr; // its own table (the two kernels may factor the length differently)
         int                       ew_kind = 0;
         int                       fused_id = 0;
         b200fft_kargs             ka{};
@@ -116,6 +117,9 @@ namespace b200fft
         unsigned long long        ntiles = 0;
         std::vector<LoopDim>      loops; // host-side loops for dimensions beyond the kernel's three
         std::string               note;
+        // when not empty: the ordinary steps this step replaces, run instead of it when a base pointer
+        // turns out not to be 16-byte aligned at execute time
+        std::vector<Step>         alt;
     };
 
     // device-resident tables owned by a plan

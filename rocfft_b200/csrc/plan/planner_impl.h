@@ -66,7 +66,20 @@ namespace b200fft
             size_t                      cnt = 0;
             const b200fft_pool2d_entry* p   = b200fft_pool2d(&cnt);
             for(size_t i = 0; i < cnt; ++i)
-                if((size_t)p[i].n0 == n0 && (size_t)p[i].n1 == n1 && p[i].base.precision == prec)
+                if((size_t)p[i].n0 == n0 && (size_t)p[i].n1 == n1 && p[i].base.precision == prec
+                   && p[i].base.variant == B200FFT_2D_SINGLE)
+                    return &p[i];
+            return nullptr;
+        }
+
+        // whole batches of n0 x n1 images through L2 in one persistent kernel, tile rows of 16 * units bytes
+        inline const b200fft_pool2d_entry* pool2d_l2_find(size_t n0, size_t n1, int prec, int units)
+        {
+            size_t                      cnt = 0;
+            const b200fft_pool2d_entry* p   = b200fft_pool2d(&cnt);
+            for(size_t i = 0; i < cnt; ++i)
+                if((size_t)p[i].n0 == n0 && (size_t)p[i].n1 == n1 && p[i].base.precision == prec
+                   && p[i].base.variant == B200FFT_2D_L2 && p[i].base.tpb == units)
                     return &p[i];
             return nullptr;
         }
@@ -591,6 +604,11 @@ namespace b200fft
                     }
                     const b200fft_pool_entry* tk
                         = tma_variant >= 0 ? pool_find(s.kernel_length ? s.kernel_length : s.n, prec_, tma_variant) : nullptr;
+                    // packed row pairs where that kernel exists (instruction-bound lengths, single precision)
+                    if(tk && !getenv("ROCFFT_B200_NO_PK"))
+                        if(const b200fft_pool_entry* pk = pool_find(s.kernel_length ? s.kernel_length : s.n, prec_,
+                                                                    tma_variant + (B200FFT_ROW_TMA_PK - B200FFT_ROW_TMA)))
+                            tk = pk;
                     const bool rows_back_to_back = o.size() <= 1 && st.loops.empty()
                                                    && (o.empty() || ((size_t)o[0].is == in_row && (size_t)o[0].os == out_row));
                     const bool offsets_ok = (s.in.byte_off[0] % 16 == 0) && (s.out.byte_off[0] % 16 == 0);
@@ -609,6 +627,8 @@ namespace b200fft
                 a.use_scale = s.use_scale;
                 a.scale     = s.scale;
                 a.twiddles  = stacked_twiddles(kern);
+                if(st.kern_unaligned)
+                    st.twiddles_unaligned = stacked_twiddles(st.kern_unaligned);
                 a.aux[0]    = s.aux0 ? s.aux0 : a.aux[0];
                 a.aux[1]    = s.aux1;
                 a.iaux[0]   = s.iaux0;
@@ -892,8 +912,100 @@ namespace b200fft
                     return;
                 }
                 size_t first = 0;
+                long long fused_l2 = -1; // index of the fused-through-L2 step, if one is emitted
+                auto emit_dim = [&](size_t d) {
+                    const DataView& src = (d == 0) ? in : out;
+                    Stage           s;
+                    s.n       = in.len[d];
+                    s.is      = src.stride[d];
+                    s.os      = out.stride[d];
+                    s.outer   = outer_of(src, out, (int)d);
+                    s.in      = src.buf;
+                    s.out     = out.buf;
+                    s.inverse = inverse;
+                    if(d == rank - 1 && use_scale)
+                    {
+                        s.use_scale = true;
+                        s.scale     = scale;
+                    }
+                    emit_c2c_1d(s);
+                };
+                // Large images: rows and columns of the two fastest dimensions in one persistent kernel
+                // that keeps the intermediate array in L2 (stockham_fused2d.cuh): one trip through device
+                // memory instead of two.  Needs contiguous interleaved images on both sides and enough
+                // of them to interleave the row pass of one image with the column pass of the previous.
+                // Measured (1024 x 1024): double precision 64 images 0.68 ms against 0.35 + 0.41 ms as two passes;
+                // single precision no gain (1.50 ms per 256 images either way: the kernel is bound on the SM
+                // side), so single precision keeps the separate passes unless ROCFFT_B200_2D_L2=1 asks for it.
+                if(rank >= 2 && !getenv("ROCFFT_B200_NO_2D_L2") && !in.buf.planar && !out.buf.planar
+                   && (prec_ == 1 || getenv("ROCFFT_B200_2D_L2")))
+                {
+                    int units = 4;
+                    if(const char* env = getenv("ROCFFT_B200_2D_L2_UNITS"))
+                        units = atoi(env);
+                    const b200fft_pool2d_entry* kl = pool2d_l2_find(in.len[0], in.len[1], prec_, units);
+                    std::vector<OuterDim> o;
+                    for(size_t k = 2; k < rank; ++k)
+                        o.push_back({out.len[k], in.stride[k], out.stride[k]});
+                    o.push_back({in.batch, in.dist, out.dist});
+                    drop_unit_dims(o);
+                    merge_dims(o);
+                    const ptrdiff_t n0 = (ptrdiff_t)in.len[0];
+                    const ptrdiff_t al = prec_ == 0 ? 2 : 1; // image strides in multiples of 16 bytes
+                    bool ok = kl && in.stride[0] == 1 && out.stride[0] == 1 && in.stride[1] == n0 && out.stride[1] == n0
+                              && (in.buf.byte_off[0] % 16 == 0) && (out.buf.byte_off[0] % 16 == 0) && !o.empty();
+                    size_t nimg = 1;
+                    for(const auto& d : o)
+                    {
+                        ok = ok && d.len > 0 && d.is > 0 && d.os > 0 && (d.is % al == 0) && (d.os % al == 0)
+                             && (unsigned long long)d.os * csize_ < (1ull << 40);
+                        nimg *= d.len;
+                    }
+                    size_t min_images = 4;
+                    if(const char* env = getenv("ROCFFT_B200_2D_L2_MIN_IMAGES"))
+                        min_images = (size_t)atoll(env);
+                    if(ok && nimg >= min_images)
+                    {
+                        // the kernel walks the images of the first outer dimension; further dimensions are host loops
+                        Step st;
+                        st.kind          = Step::TILE;
+                        st.kern          = &kl->base;
+                        st.in            = in.buf;
+                        st.out           = out.buf;
+                        b200fft_kargs& a = st.ka;
+                        a.in.es = a.out.es = n0;
+                        for(int k = 0; k < 3; ++k)
+                        {
+                            a.on[k]    = 1;
+                            a.in.os[k] = a.out.os[k] = 0;
+                        }
+                        a.in.os[0] = a.out.os[0] = 1;
+                        a.on[0]    = (unsigned)n0;
+                        a.on[1]    = (unsigned)o[0].len;
+                        a.in.os[1] = o[0].is;
+                        a.out.os[1] = o[0].os;
+                        for(size_t k = 1; k < o.size(); ++k)
+                            st.loops.push_back({o[k].len, o[k].is, o[k].os});
+                        a.ntile0    = 1;
+                        a.inverse   = inverse;
+                        a.use_scale = rank == 2 && use_scale;
+                        a.scale     = scale;
+                        a.twiddles  = stacked_twiddles(kl->n0, kl->base.factors, kl->base.nfactors);
+                        std::vector<char> zeros(sizeof(int) * o[0].len, 0);
+                        a.aux[1]    = upload(zeros); // per-image counters of finished row tiles
+                        a.aux[3]    = device_error_flag();
+                        st.ntiles   = o[0].len; // images per launch
+                        // misaligned base pointers at execute time: rows then columns as separate passes
+                        st.in_elem_bytes  = elem_bytes(in.buf);
+                        st.out_elem_bytes = elem_bytes(out.buf);
+                        st.note           = kl->base.name;
+                        fused_l2          = (long long)core_.steps.size();
+                        core_.steps.push_back(st);
+                        first = 2;
+                    }
+                }
                 // the two fastest dimensions in one kernel when the pool has the pair: one pass instead of two
-                if(rank >= 2 && !getenv("ROCFFT_B200_NO_2D_SINGLE"))
+                if(first == 0 && rank >= 2 && !getenv("ROCFFT_B200_NO_2D_SINGLE"))
                     if(const b200fft_pool2d_entry* k2 = pool2d_find(in.len[0], in.len[1], prec_))
                     {
                         std::vector<OuterDim> o;
@@ -933,22 +1045,17 @@ namespace b200fft
                         first = 2;
                     }
                 for(size_t d = first; d < rank; ++d)
+                    emit_dim(d);
+                if(fused_l2 >= 0)
                 {
-                    const DataView& src = (d == 0) ? in : out;
-                    Stage           s;
-                    s.n       = in.len[d];
-                    s.is      = src.stride[d];
-                    s.os      = out.stride[d];
-                    s.outer   = outer_of(src, out, (int)d);
-                    s.in      = src.buf;
-                    s.out     = out.buf;
-                    s.inverse = inverse;
-                    if(d == rank - 1 && use_scale)
-                    {
-                        s.use_scale = true;
-                        s.scale     = scale;
-                    }
-                    emit_c2c_1d(s);
+                    // the fused kernel's copy engines need 16-byte aligned bases: for other pointers the step
+                    // carries the two ordinary passes it replaces (built here, run instead of it at execute time)
+                    const size_t mark = core_.steps.size();
+                    emit_dim(0);
+                    emit_dim(1);
+                    std::vector<Step> alt(core_.steps.begin() + (ptrdiff_t)mark, core_.steps.end());
+                    core_.steps.erase(core_.steps.begin() + (ptrdiff_t)mark, core_.steps.end());
+                    core_.steps[(size_t)fused_l2].alt = std::move(alt);
                 }
             }
 

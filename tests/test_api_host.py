@@ -127,18 +127,36 @@ def test_cache_exports_are_inert(L):
     assert L.rocfft_cache_buffer_free(buf) == rf.rocfft_status_success
 
 
-def test_planner_choices_for_benchmark_configs(L):
+def test_planner_choices_for_benchmark_configs(L, monkeypatch):
     # config 1: one row kernel, no work buffer
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [4096], 16384)
     text = describe(L, p)
     assert "steps: 1" in text and "len4096" in text and p.work_bytes == 0
-    # config 3: row pass then in-place column pass, no transposes, no work buffer
+    # config 3: rows and columns of every image in one kernel that keeps the intermediate in L2; no work buffer
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 64)
+    text = describe(L, p)
+    assert "steps: 1" in text and "fft2d_l2_dp_1024x1024" in text and p.work_bytes == 0
+    # config 5: three in-place passes (rows, then the TMA-fed column kernel twice), no transposes, no work buffer;
+    # in single precision the fused kernel is opt-in (measured: no gain)
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
+    text = describe(L, p)
+    assert "steps: 3" in text and text.count("col_tma") == 2 and p.work_bytes == 0
+    monkeypatch.setenv("ROCFFT_B200_2D_L2", "1")
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
+    text = describe(L, p)
+    assert "steps: 2" in text and "fft2d_l2_sp_1024x1024" in text and "col_tma" in text and p.work_bytes == 0
+    monkeypatch.delenv("ROCFFT_B200_2D_L2")
+    # without the fused kernel: a row pass and in-place column passes
+    monkeypatch.setenv("ROCFFT_B200_NO_2D_L2", "1")
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 64)
     text = describe(L, p)
     assert "steps: 2" in text and "col" in text and p.work_bytes == 0
-    # config 5: three in-place passes
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
     assert "steps: 3" in describe(L, p) and p.work_bytes == 0
+    monkeypatch.delenv("ROCFFT_B200_NO_2D_L2")
+    # a single image is not worth the interleaved schedule
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 1)
+    assert "steps: 2" in describe(L, p)
     # config 4: prime length goes through the single-kernel Bluestein with M = 20480
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)
     text = describe(L, p)
