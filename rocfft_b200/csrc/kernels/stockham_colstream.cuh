@@ -133,17 +133,55 @@ namespace b200fft
 
     // UN = 16-byte units per tile row: 8 (128-byte rows, the width strided HBM traffic wants) or 4
     // (64-byte rows: half the shared memory, for tiles that come out of L2)
-    template <class C, int UN = 8>
+    // Single precision, one column per thread: twice the threads of the packed form for the same tile
+    // (more warps to hide the latencies of each phase), ordinary scalar arithmetic, 8-byte units.
+    struct StreamValScalarF
+    {
+        using P                  = float;
+        using C2                 = float2;
+        using U                  = float2;
+        static constexpr int VEC = 1;
+        __device__ static __forceinline__ C2 unpack(const float2 v, float sgn)
+        {
+            return make_float2(v.x, v.y * sgn);
+        }
+        __device__ static __forceinline__ float2 pack(const C2 c, float sx, float sy)
+        {
+            return make_float2(c.x * sx, c.y * sy);
+        }
+        __device__ static __forceinline__ C2 twmul(const C2 c, const float2 w)
+        {
+            return cmul(c, w);
+        }
+        using TWS = float2;
+        __device__ static __forceinline__ TWS tws(const float2 w)
+        {
+            return w;
+        }
+    };
+    template <typename T, bool SC>
+    struct StreamValSel
+    {
+        using type = StreamVal<T>;
+    };
+    template <>
+    struct StreamValSel<float, true>
+    {
+        using type = StreamValScalarF;
+    };
+
+    // SC: single precision in scalar form (one column per thread) instead of packed pairs
+    template <class C, int UN = 8, bool SC = false>
     struct ColStream
     {
         using Cfg                        = C;
         using T                          = typename C::T;
-        using SV                         = StreamVal<T>;
+        using SV                         = typename StreamValSel<T, SC>::type;
         using P                          = typename SV::P;
         using C2                         = typename SV::C2;
         using U                          = typename SV::U;
         static constexpr int VEC         = SV::VEC;
-        static constexpr int UNITS       = UN; // 16-byte units per row segment
+        static constexpr int UNITS       = UN * 16 / (int)sizeof(U); // per-thread units in a row segment of UN * 16 bytes
         static constexpr int COLS        = UNITS * VEC;
         static constexpr int THREADS     = C::TPT * UNITS;
         static constexpr int EPT         = C::N / C::TPT;
@@ -152,13 +190,13 @@ namespace b200fft
         static constexpr unsigned ROW_BYTES   = (unsigned)UN * 16u;
         static constexpr unsigned STAGE_BYTES = (unsigned)C::N * ROW_BYTES;
         static constexpr int      XROWS       = C::N + (C::N >> 5) + 1; // one pad row per 32 keeps both passes conflict-free
-        static constexpr size_t   XCHG_BYTES  = C::NPASS > 1 ? (size_t)XROWS * UNITS * 8 : 0;
+        static constexpr size_t   XCHG_BYTES  = C::NPASS > 1 ? (size_t)XROWS * UNITS * sizeof(P) : 0;
         // two-pass kernels keep the twiddles of their second pass in shared memory (16 bytes per entry):
         // the L1 cache left beside ~200 KB of shared memory is too small to hold them against the
         // kernel's own store traffic
         static constexpr bool     TW_SMEM     = C::NPASS == 2;
         static constexpr int      TW_ENTRIES  = TW_SMEM ? (C::FL::get(1) - 1) * C::FL::get(0) : 0;
-        static constexpr size_t   TW_BYTES    = (size_t)TW_ENTRIES * 16;
+        static constexpr size_t   TW_BYTES    = (size_t)TW_ENTRIES * sizeof(typename SV::TWS);
         static constexpr size_t   SMEM_BYTES  = 256 + STAGE_BYTES + XCHG_BYTES + 16 + TW_BYTES; // slack to align the stage to 256 bytes
         static_assert((C::N & (C::N - 1)) == 0 && C::N >= 32, "power-of-two lengths only");
         __device__ static __forceinline__ int prow(int e)
@@ -298,11 +336,11 @@ namespace b200fft
     // kargs as for the other column kernels; aux[3] = device error flag (int*).  `map` describes
     // the input array: dimension 0 = 8-byte elements along the columns, 1 = the transform,
     // 2 / 3 = the outer dimensions on[1] / on[2].
-    template <class C, bool BLK>
-    __global__ void __launch_bounds__(ColStream<C>::THREADS, C::MINB)
+    template <class C, bool BLK, bool SC = false>
+    __global__ void __launch_bounds__((ColStream<C, 8, SC>::THREADS), C::MINB)
         stockham_colstream_kernel(const __grid_constant__ b200fft_kargs a, const __grid_constant__ CUtensorMap map)
     {
-        using CC = ColStream<C>;
+        using CC = ColStream<C, 8, SC>;
         using T  = typename C::T;
         using T2 = typename C::T2;
         using U  = typename CC::U;
@@ -468,10 +506,10 @@ namespace b200fft
         return fn;
     }
 
-    template <class C, bool BLK>
+    template <class C, bool BLK, bool SC = false>
     cudaError_t launch_colstream_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
-        using CC                      = ColStream<C>;
+        using CC                      = ColStream<C, 8, SC>;
         using T2                      = typename C::T2;
         static int        blocks_per_sm[64] = {};
         static int        sm_count[64]      = {};
@@ -480,7 +518,7 @@ namespace b200fft
         cudaGetDevice(&dev);
         if(dev < 0 || dev >= 64)
             return cudaErrorInvalidDevice;
-        auto kern = stockham_colstream_kernel<C, BLK>;
+        auto kern = stockham_colstream_kernel<C, BLK, SC>;
         {
             std::lock_guard<std::mutex> g(mtx);
             if(!blocks_per_sm[dev])

@@ -93,6 +93,7 @@ namespace b200fft
             int        rank  = 0;
             size_t     csize = 8;
             size_t     nx = 1, ny = 1, nz = 1;
+            size_t     nb = 1; // transforms per plan (batch); every rank holds its slab of each
             size_t     lz = 1, ly = 1; // local extents: nz / P, ny / P
             int        chunks = 1;
             size_t     slab_bytes = 0;
@@ -110,6 +111,11 @@ namespace b200fft
             std::vector<void*> peer_r, peer_r2; // every rank's buffers as mapped here
             void **            tab_a = nullptr, **tab_b = nullptr; // device tables of block bases
             int*               bar   = nullptr; // device words for the barrier all-reduce
+            // Output split along X instead of Z (the reference's "slow in, fast out" layout): one global
+            // transpose instead of two.  passA = X rows into the plan-owned array S, passB = Y columns stored
+            // straight into the peers' R (one launch per destination), passC = Z columns from R to the caller.
+            bool  xsplit = false;
+            void* S      = nullptr;
         };
 
         size_t total_work(const SlabPlan& sp)
@@ -176,20 +182,24 @@ namespace b200fft
         sp->csize = plan->precision == rocfft_precision_single ? 8 : 16;
         const int P = sp->P;
 
-        // The optimised plan takes rank-3, batch-1 complex transforms whose fields are one contiguous
-        // Z-slab per rank, in rank order, with lengths divisible by the number of ranks.  Everything
-        // else goes through the gather / scatter plan; all ranks must take the same branch, so they
-        // agree on it first.
+        // The optimised plan takes rank-3 complex transforms (any batch) whose fields are one contiguous
+        // Z-slab per rank — the slabs of the batch members back to back — in rank order, with lengths
+        // divisible by the number of ranks.  Everything else goes through the gather / scatter plan; all
+        // ranks must take the same branch, so they agree on it first.
         const bool c2c = plan->transformType == rocfft_transform_type_complex_forward
                          || plan->transformType == rocfft_transform_type_complex_inverse;
         bool slab_ok = c2c && d.inArrayType == rocfft_array_type_complex_interleaved
-                       && d.outArrayType == rocfft_array_type_complex_interleaved && plan->rank == 3 && plan->batch == 1
+                       && d.outArrayType == rocfft_array_type_complex_interleaved && plan->rank == 3 && plan->batch >= 1
                        && plan->lengths == plan->userLengths;
+        // the NCCL send/recv exchange moves one transform's slab; batches use the peer-store exchange
+        if(plan->batch > 1 && getenv("ROCFFT_B200_MGPU_NCCL"))
+            slab_ok = false;
         if(slab_ok)
         {
             sp->nx  = plan->lengths[0];
             sp->ny  = plan->lengths[1];
             sp->nz  = plan->lengths[2];
+            sp->nb  = plan->batch;
             slab_ok = sp->nz % P == 0 && sp->ny % P == 0;
         }
         if(slab_ok)
@@ -203,17 +213,38 @@ namespace b200fft
                 if(b.lower.size() != 4 || b.upper.size() != 4 || b.stride.size() != 4)
                     return false;
                 const size_t lo[4] = {0, 0, sp->rank * sp->lz, 0};
-                const size_t hi[4] = {sp->nx, sp->ny, (sp->rank + 1) * sp->lz, 1};
+                const size_t hi[4] = {sp->nx, sp->ny, (sp->rank + 1) * sp->lz, sp->nb};
                 const size_t st[4] = {1, sp->nx, sp->nx * sp->ny, sp->nx * sp->ny * sp->lz};
                 for(int i = 0; i < 4; ++i)
-                    if(b.lower[i] != lo[i] || b.upper[i] != hi[i] || (i < 3 && b.stride[i] != st[i]))
+                    if(b.lower[i] != lo[i] || b.upper[i] != hi[i] || ((i < 3 || sp->nb > 1) && b.stride[i] != st[i]))
                         return false;
                 return true;
             };
-            slab_ok = is_slab(d.inFields[0]) && is_slab(d.outFields[0]);
+            const bool in_slab = is_slab(d.inFields[0]);
+            // output split along the fastest dimension: rank q holds x in [q*lx, (q+1)*lx) of every row
+            auto is_xsplit = [&](const rocfft_field_t& f) {
+                if(f.bricks.size() != 1 || sp->nx % P != 0 || getenv("ROCFFT_B200_MGPU_NCCL"))
+                    return false;
+                const rocfft_brick_t& b = f.bricks[0];
+                if(b.lower.size() != 4 || b.upper.size() != 4 || b.stride.size() != 4)
+                    return false;
+                const size_t lx    = sp->nx / P;
+                const size_t lo[4] = {sp->rank * lx, 0, 0, 0};
+                const size_t hi[4] = {(sp->rank + 1) * lx, sp->ny, sp->nz, sp->nb};
+                const size_t st[4] = {1, lx, lx * sp->ny, lx * sp->ny * sp->nz};
+                for(int i = 0; i < 4; ++i)
+                    if(b.lower[i] != lo[i] || b.upper[i] != hi[i] || ((i < 3 || sp->nb > 1) && b.stride[i] != st[i]))
+                        return false;
+                return true;
+            };
+            // (with a single rank both descriptions fit; the two-transpose plan is kept unless a test asks otherwise)
+            const bool out_slab = is_slab(d.outFields[0]);
+            sp->xsplit = in_slab && is_xsplit(d.outFields[0]) && (!out_slab || getenv("ROCFFT_B200_MGPU_PREFER_XSPLIT"));
+            slab_ok    = in_slab && (sp->xsplit || out_slab);
         }
         {
-            int  mine = slab_ok ? 1 : 0;
+            // 0: not a slab layout, 1: slabs in and out, 2: slabs in, X-split out; every rank must say the same
+            int  mine = slab_ok ? (sp->xsplit ? 2 : 1) : 0;
             int* dbuf = nullptr;
             if(cudaMalloc(&dbuf, sizeof(int) * (P + 1)) != cudaSuccess)
                 throw std::runtime_error("cudaMalloc failed");
@@ -227,7 +258,7 @@ namespace b200fft
             if(e != cudaSuccess)
                 throw std::runtime_error("brick exchange failed");
             for(int v : all)
-                slab_ok = slab_ok && v;
+                slab_ok = slab_ok && v == mine && v != 0;
         }
         if(!slab_ok && !getenv("ROCFFT_B200_MGPU_NO_GATHER"))
         {
@@ -253,7 +284,8 @@ namespace b200fft
 
         const size_t nx = sp->nx, ny = sp->ny, lz = sp->lz, ly = sp->ly;
         const size_t cz = lz / k, cy = ly / k;
-        const size_t slab_elems = nx * ny * lz;
+        const size_t slab_elems = nx * ny * lz; // one batch member's slab
+        const size_t nb         = sp->nb;
         sp->slab_bytes          = slab_elems * sp->csize;
         const int  prec         = plan->precision == rocfft_precision_single ? 0 : 1;
         const bool inverse      = plan->transformType == rocfft_transform_type_complex_inverse;
@@ -269,9 +301,9 @@ namespace b200fft
         // work buffer: S | R | R2, then whatever scratch the passes ask for (none today)
         auto align = [](size_t v) { return (v + 255) & ~size_t(255); };
         sp->off_s  = 0;
-        sp->off_r  = align(sp->slab_bytes);
-        sp->off_r2 = sp->off_r + align(sp->slab_bytes);
-        sp->work_bytes = sp->off_r2 + align(sp->slab_bytes);
+        sp->off_r  = align(sp->slab_bytes * nb);
+        sp->off_r2 = sp->off_r + align(sp->slab_bytes * nb);
+        sp->work_bytes = sp->off_r2 + align(sp->slab_bytes * nb);
 
         BufRef user_in, user_out, S, R, R2;
         user_in.id  = BUF_USER_IN;
@@ -286,9 +318,13 @@ namespace b200fft
             if(cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
                 sp->p2p = false; // no GPU in this process: the plan stays inspectable only
         }
+        if(sp->xsplit && !sp->p2p)
+            throw std::runtime_error("the single-transpose plan needs a GPU and the peer-store exchange");
+        if(sp->xsplit && cudaMalloc(&sp->S, sp->slab_bytes * nb) != cudaSuccess)
+            throw std::runtime_error("intermediate array allocation failed");
         if(sp->p2p)
         {
-            if(cudaMalloc(&sp->R, sp->slab_bytes) != cudaSuccess || cudaMalloc(&sp->R2, sp->slab_bytes) != cudaSuccess)
+            if(cudaMalloc(&sp->R, sp->slab_bytes * nb) != cudaSuccess || cudaMalloc(&sp->R2, sp->slab_bytes * nb) != cudaSuccess)
                 throw std::runtime_error("exchange buffer allocation failed");
             sp->peer_r.assign(P, nullptr);
             sp->peer_r2.assign(P, nullptr);
@@ -351,6 +387,76 @@ namespace b200fft
             sp->work_bytes = 0;
         }
 
+        if(sp->xsplit)
+        {
+            const size_t lx = nx / P;
+            BufRef       Sb, Rb;
+            Sb.id = Rb.id  = BUF_ABS;
+            Sb.byte_off[0] = reinterpret_cast<size_t>(sp->S);
+            Rb.byte_off[0] = reinterpret_cast<size_t>(sp->R);
+            // pass A: FFT along X (rows) of the local slab(s): caller's input -> S, same layout
+            {
+                auto    core = new_core();
+                Planner p(*core);
+                Stage   s;
+                s.n  = nx;
+                s.is = s.os = 1;
+                s.outer.push_back({ny, (ptrdiff_t)nx, (ptrdiff_t)nx});
+                s.outer.push_back({lz, (ptrdiff_t)(nx * ny), (ptrdiff_t)(nx * ny)});
+                s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)slab_elems});
+                s.in      = user_in;
+                s.out     = Sb;
+                s.inverse = inverse;
+                p.emit_c2c_1d(s);
+                sp->passA.push_back(std::move(core));
+            }
+            // pass B: FFT along Y; the columns x in [q*lx, (q+1)*lx) go to rank q, which receives
+            // R[b][z][y][x_local] with z = rank*lz + z_local: one launch per destination, plain peer stores
+            {
+                auto    core = new_core();
+                Planner p(*core);
+                for(int q = 0; q < P; ++q)
+                {
+                    Stage s;
+                    s.n  = ny;
+                    s.is = (ptrdiff_t)nx;
+                    s.os = (ptrdiff_t)lx;
+                    s.outer.push_back({lx, 1, 1});
+                    s.outer.push_back({lz, (ptrdiff_t)(nx * ny), (ptrdiff_t)(ny * lx)});
+                    s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)(sp->nz * ny * lx)});
+                    s.in             = Sb;
+                    s.in.byte_off[0] = reinterpret_cast<size_t>(sp->S) + (size_t)q * lx * sp->csize;
+                    s.out            = Rb;
+                    s.out.byte_off[0]
+                        = reinterpret_cast<size_t>(sp->peer_r[q]) + (size_t)sp->rank * lz * ny * lx * sp->csize;
+                    s.inverse = inverse;
+                    p.emit_c2c_1d(s);
+                }
+                sp->passB.push_back(std::move(core));
+            }
+            // pass C: FFT along Z on R[b][z][y][x_local] -> the caller's X-split brick (same index order)
+            {
+                auto    core = new_core();
+                Planner p(*core);
+                Stage   s;
+                s.n  = sp->nz;
+                s.is = (ptrdiff_t)(ny * lx);
+                s.os = (ptrdiff_t)(ny * lx);
+                s.outer.push_back({ny * lx, 1, 1});
+                s.outer.push_back({nb, (ptrdiff_t)(sp->nz * ny * lx), (ptrdiff_t)(sp->nz * ny * lx)});
+                s.in      = Rb;
+                s.out     = user_out;
+                s.inverse = inverse;
+                if(d.scale != 1.0)
+                {
+                    s.use_scale = true;
+                    s.scale     = d.scale;
+                }
+                p.emit_c2c_1d(s);
+                sp->passC.push_back(std::move(core));
+            }
+        }
+        else
         for(int c = 0; c < k; ++c)
         {
             // ---- pass A: FFT along Y for z-chunk c, slab -> S_c[q][zc][yq][x]
@@ -365,6 +471,8 @@ namespace b200fft
                 s.out_bs  = (ptrdiff_t)(cz * ly * nx);
                 s.outer.push_back({nx, 1, 1});
                 s.outer.push_back({cz, (ptrdiff_t)(nx * ny), (ptrdiff_t)(ly * nx)});
+                // batch members: slab after slab on the input side, T after T (nz * ly * nx points each) in the receive buffers
+                s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)slab_elems});
                 s.in             = user_in;
                 s.in.byte_off[0] = c * cz * nx * ny * sp->csize;
                 s.out            = S;
@@ -387,6 +495,7 @@ namespace b200fft
                 s.out_bs  = (ptrdiff_t)(lz * cy * nx);
                 s.outer.push_back({nx, 1, 1});
                 s.outer.push_back({cy, (ptrdiff_t)nx, (ptrdiff_t)nx});
+                s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)slab_elems});
                 s.in              = R;
                 s.in.byte_off[0]  = sp->off_r + c * cy * nx * sp->csize;
                 s.out             = S;
@@ -407,6 +516,7 @@ namespace b200fft
                 s.outer.push_back({cy, (ptrdiff_t)nx, (ptrdiff_t)nx});
                 s.outer.push_back({(size_t)P, (ptrdiff_t)(lz * cy * nx), (ptrdiff_t)(ly * nx)});
                 s.outer.push_back({lz, (ptrdiff_t)(cy * nx), (ptrdiff_t)(nx * ny)});
+                s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)slab_elems});
                 s.in              = R2;
                 s.in.byte_off[0]  = sp->off_r2 + c * chunk_bytes;
                 s.out             = user_out;
@@ -484,6 +594,7 @@ namespace b200fft
                 if(nccl().AllReduce(sp->bar + 2, sp->bar + 10, 1, ncclInt, ncclSum, sp->comm, nullptr) == ncclSuccess)
                     cudaStreamSynchronize(nullptr);
             }
+            cudaFree(sp->S);
             cudaFree(sp->tab_a);
             cudaFree(sp->tab_b);
             cudaFree(sp->bar);
@@ -511,7 +622,8 @@ namespace b200fft
             return "";
         std::ostringstream o;
         o << "slab plan: ranks " << sp->P << " rank " << sp->rank << " lengths " << sp->nx << "x" << sp->ny << "x"
-          << sp->nz << " chunks " << sp->chunks << " work bytes " << sp->work_bytes << "\n";
+          << sp->nz << " batch " << sp->nb << (sp->xsplit ? " output split along x (one global transpose)" : "")
+          << " chunks " << sp->chunks << " work bytes " << sp->work_bytes << "\n";
         for(int c = 0; c < sp->chunks; ++c)
         {
             o << "chunk " << c << " pass A (Y):\n" << describe_core(*sp->passA[c]);
@@ -591,6 +703,8 @@ namespace b200fft
             mark(1);
             if(sp->P > 1)
             {
+                // (single-transpose plan: this barrier also tells every rank that the others have finished
+                // reading their R of the previous call, which pass B is about to overwrite)
                 flag(0);
                 if(!barrier(0))
                     return rocfft_status_failure; // the communicator itself is broken: nothing more can be enqueued

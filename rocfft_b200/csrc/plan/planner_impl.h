@@ -512,8 +512,10 @@ namespace b200fft
                 const long long pitch_bytes = std::llabs(a.in.es) * 8;
                 const bool      prefer_cluster
                     = prec_ == 0 && s.n <= 1024 && (s.n >= 1024 || (s.n >= 512 && pitch_bytes >= (1ll << 20)));
+                // (stores into peer GPUs' buffers keep the cluster kernel: measured on two GPUs, 1024^3, passes A / B
+                // 3.04 ms with it against 3.20 ms with the TMA-fed kernel)
                 const bool prefer_tma = !getenv("ROCFFT_B200_NO_COLTMA") && !getenv("ROCFFT_B200_COLCLUSTER")
-                                        && (s.n == 1024 || getenv("ROCFFT_B200_COLTMA"));
+                                        && ((s.n == 1024 && !s.out_blk_ptrs) || getenv("ROCFFT_B200_COLTMA"));
                 if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
                    && (prefer_tma || getenv("ROCFFT_B200_COLCLUSTER")
                        || ((s.out_blk_ptrs || prefer_cluster) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))

@@ -12,12 +12,14 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _launch(nproc, lengths, prec, direction, placement, port):
+def _launch(nproc, lengths, prec, direction, placement, port, batch=1, out_split="z"):
     env = dict(os.environ)
     env["NCCL_NVLS_ENABLE"] = "0"
+    if out_split == "x":
+        env["ROCFFT_B200_MGPU_PREFER_XSPLIT"] = "1"  # a single rank fits both layouts: take the one under test
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mgpu_worker.py"),
-           lengths, prec, direction, placement]
+           lengths, prec, direction, placement, str(batch), out_split]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
@@ -40,6 +42,16 @@ def test_two_rank_slab_plan(gpu, lengths, prec, direction, placement):
     if gpu.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _launch(2, lengths, prec, direction, placement, 29632)
+
+
+@pytest.mark.parametrize("lengths,prec,direction,placement,batch", [
+    ("64x32x16", "single", "fwd", "ip", 4),     # the reference's multi-device tests use batch 4 and 1
+    ("32x64x32", "double", "inv", "op", 3),
+])
+def test_batched_slab_plan(gpu, lengths, prec, direction, placement, batch):
+    """Batches through the optimised slab plan (reference: clients/tests/multi_device_test.cpp:55-63, batch {4, 1});
+    one rank when a single GPU is present, two across NVLink otherwise."""
+    _launch(min(2, gpu.cuda.device_count()), lengths, prec, direction, placement, 29633, batch)
 
 
 @pytest.mark.parametrize("split", ["slowest_both", "slow_in_fast_out", "pencils"])
@@ -71,3 +83,14 @@ def test_multi_process_general_layouts(gpu, case):
     """Layouts outside the optimised slab plan run as gather -> transform on rank 0 -> scatter over NCCL;
     with one GPU the same path runs with a single-rank communicator."""
     _launch_fields(min(2, gpu.cuda.device_count()), case, 29641)
+
+
+@pytest.mark.parametrize("lengths,prec,direction,placement,batch", [
+    ("64x32x16", "single", "fwd", "op", 1),
+    ("64x64x64", "single", "fwd", "ip", 1),
+    ("32x32x64", "double", "inv", "op", 4),
+])
+def test_slab_in_x_split_out_single_transpose(gpu, lengths, prec, direction, placement, batch):
+    """Input split along the slowest dimension, output along the fastest (the reference's SLOW_IN_FAST_OUT,
+    clients/tests/multi_device_test.cpp:117-123): the optimised plan then needs one global transpose, not two."""
+    _launch(min(2, gpu.cuda.device_count()), lengths, prec, direction, placement, 29634, batch, "x")
