@@ -23,12 +23,20 @@
 
 namespace
 {
-    // ---- logging (ROCFFT_LAYER bitmask: 1 trace, 2 bench, 4 profile, 8 plan; include/logging.h:139-150,
-    // auxiliary.cpp:83-137 in the reference) ----
+    // ---- logging (ROCFFT_LAYER bitmask: 1 trace, 2 bench, 4 profile, 8 plan, 16 kernelio, 128 graph;
+    // include/logging.h:139-150, auxiliary.cpp:83-137 in the reference) ----
     struct Log
     {
         int           layer = 0;
-        std::ofstream trace_file, plan_file, bench_file, profile_file;
+        std::ofstream trace_file, plan_file, bench_file, profile_file, kernelio_file, graph_file;
+        std::ostream& kernelio()
+        {
+            return kernelio_file.is_open() ? (std::ostream&)kernelio_file : std::cerr;
+        }
+        std::ostream& graph()
+        {
+            return graph_file.is_open() ? (std::ostream&)graph_file : std::cerr;
+        }
         std::mutex    mtx;
         std::ostream& trace()
         {
@@ -63,6 +71,12 @@ namespace
             if(const char* p = getenv("ROCFFT_LOG_PROFILE_PATH"))
                 if(!profile_file.is_open())
                     profile_file.open(p, std::ios::app);
+            if(const char* p = getenv("ROCFFT_LOG_KERNELIO_PATH"))
+                if(!kernelio_file.is_open())
+                    kernelio_file.open(p, std::ios::app);
+            if(const char* p = getenv("ROCFFT_LOG_GRAPH_PATH"))
+                if(!graph_file.is_open())
+                    graph_file.open(p, std::ios::app);
         }
     };
     Log& log()
@@ -530,6 +544,12 @@ rocfft_status rocfft_plan_create(rocfft_plan*                  plan,
             if(p->core)
                 log().plan() << b200fft::describe_core(*p->core) << std::endl;
         }
+        if((log().layer & 128) && p->mgpu)
+        {
+            // graph layer: the multi-device plan as a graphviz digraph (reference: library/src/transform.cpp:178-254)
+            std::lock_guard<std::mutex> g(log().mtx);
+            log().graph() << b200fft::multi_device_plan_graph(p) << std::endl;
+        }
         return rocfft_status_success;
     }
     catch(rocfft_status s)
@@ -732,6 +752,59 @@ rocfft_status rocfft_execute(const rocfft_plan     plan,
             }
             for(auto& e : ev)
                 cudaEventDestroy(e);
+            return st;
+        }
+        if(log().layer & 16)
+        {
+            // kernelio layer: a checksum of what every kernel left in its output buffer (this synchronises the stream).
+            // The reference dumps and hashes each kernel's input and output (library/src/powX.cpp:743-780, 910-956);
+            // here one order-independent 64-bit sum per kernel over the extent of its output view is written, which is
+            // what run-to-run comparisons need.
+            struct Ctx
+            {
+                unsigned long long* dev;
+                size_t              n;
+                std::vector<size_t> bytes;
+            } ctx{nullptr, core.steps.size(), std::vector<size_t>(core.steps.size(), 0)};
+            if(cudaMalloc(&ctx.dev, sizeof(unsigned long long) * std::max<size_t>(ctx.n, 1)) != cudaSuccess)
+                return rocfft_status_failure;
+            auto obs = [](void* c, size_t i, const b200fft::Step& sp, void* out_ptr, cudaStream_t s) {
+                Ctx* x = static_cast<Ctx*>(c);
+                if(i >= x->n || !out_ptr)
+                    return;
+                // extent of the output view in elements: 1 + sum (len - 1) * |stride| over the kernel's dimensions
+                const bool tile = sp.kind != b200fft::Step::EW;
+                const b200fft_ioview& v = tile ? sp.ka.out : sp.ea.out;
+                const unsigned*       on = tile ? sp.ka.on : sp.ea.on;
+                unsigned long long n0 = tile ? (sp.kern ? (unsigned long long)sp.kern->length : 1) : sp.ea.n;
+                if(tile && sp.kern && sp.kern->variant == B200FFT_2D_L2)
+                    n0 = (unsigned long long)sp.ka.on[0] * sp.ka.on[0];
+                if(v.blk >= 2 || v.planar)
+                    return; // per-rank blocks and planar outputs are not one byte range
+                unsigned long long el = 1 + (n0 ? n0 - 1 : 0) * (unsigned long long)std::llabs(v.es);
+                for(int k = 0; k < 3; ++k)
+                    el += (unsigned long long)(on[k] ? on[k] - 1 : 0) * (unsigned long long)std::llabs(v.os[k]);
+                for(const auto& l : sp.loops)
+                    el += (unsigned long long)(l.count ? l.count - 1 : 0) * (unsigned long long)std::llabs(l.out_stride);
+                x->bytes[i] = (size_t)el * sp.out_elem_bytes;
+                b200fft_launch_hash(out_ptr, x->bytes[i], x->dev + i, s);
+            };
+            rocfft_status st = b200fft::execute_core(core, in_buffer, out_buffer, work, ei.stream, nullptr, obs, &ctx);
+            if(own_alloc)
+                cudaFreeAsync(work, ei.stream);
+            cudaStreamSynchronize(ei.stream);
+            std::vector<unsigned long long> h(std::max<size_t>(ctx.n, 1), 0);
+            cudaMemcpy(h.data(), ctx.dev, sizeof(unsigned long long) * ctx.n, cudaMemcpyDeviceToHost);
+            cudaFree(ctx.dev);
+            std::lock_guard<std::mutex> g(log().mtx);
+            for(size_t i = 0; i < ctx.n; ++i)
+            {
+                log().kernelio() << "--- --- kernel " << i << " (" << core.steps[i].note << ") output: ";
+                if(ctx.bytes[i])
+                    log().kernelio() << ctx.bytes[i] << " bytes, hash " << std::hex << h[i] << std::dec << std::endl;
+                else
+                    log().kernelio() << "not hashed (blocked or planar layout)" << std::endl;
+            }
             return st;
         }
         rocfft_status st = b200fft::execute_core(core, in_buffer, out_buffer, work, ei.stream);

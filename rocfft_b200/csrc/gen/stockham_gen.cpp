@@ -139,9 +139,10 @@ namespace
         // packed pairs, measured (65536 rows): 10.10.5 with 50 threads per pair, one pair per CTA, six CTAs
         // per SM: r2c 0.150 ms, c2r 0.150 ms (scalar 20.25 kernels: 0.161 / 0.158 ms; packed 20.25: 0.170-0.181 ms)
         {500, 0, {20, 25}, 25, 8, 4, 2, 6, {10, 10, 5}, 50, 1, 6},
-        // 20480 (padded length of the 10007-point Bluestein transform): the radix-20 pass first, measured
-        // 0.431 ms per 4096 rows against 0.486 ms for 32.32.20 (16.16.16.5: 0.456, 1024 threads: 0.59-0.73)
-        {20480, 0, {20, 32, 32}, 640, 1, 1, 0, 0, {}, 0, 0, 0},
+        // 20480 (padded length of the 10007-point Bluestein transform) keeps 32.32.20 with 640 threads: as a plain
+        // row transform 20.32.32 is faster (0.431 against 0.486 ms per 4096 rows; 16.16.16.5: 0.456; 1024 threads:
+        // 0.59-0.73), but inside the fused Bluestein kernel it is slower (1.07 against 1.00 ms), and the pool has one
+        // factor order per length
     };
     const Tuned* tuned_for(int n, int prec)
     {
@@ -461,11 +462,11 @@ int main(int argc, char** argv)
                 {
                     // stage (n rows x 128 bytes) + half-tile exchange buffer + alignment slack
                     tpb = 128 / esz;
-                    sm  = 256 + (size_t)n * 128 + (size_t)(n + (n >> 5) + 1) * 64 + 16 + (size_t)(kf[1] - 1) * kf[0] * 16;
+                    sm  = 256 + (size_t)n * 128 + (size_t)(n + (n >> 5) + 1) * 64 + 16 + (size_t)(kf[1] - 1) * kf[0] * esz;
                 }
                 else if(sm > smem_cap)
                     continue;
-                const int threads = clv ? kt * 4 : streamv ? kt * 8 : pairv ? tpt * tpb / 2 : pkv ? kt * tpb : tpt * tpb;
+                const int threads = clv ? kt * 4 : streamv ? kt * (128 / esz) : pairv ? tpt * tpb / 2 : pkv ? kt * tpb : tpt * tpb;
                 int       minb    = std::max(1, 65536 / (threads * (push ? 170 : (streamv || pkv) ? 255 : (pairv || clv) ? 128 : regcap)));
                 if(push)
                     minb = std::min(minb, 4);
@@ -641,7 +642,10 @@ int main(int argc, char** argv)
         else if(k.variant == 13 || k.variant == 14)
             o << "launch_colpair_kernel<" << k.cfg << ", " << (k.variant == 14 ? "true" : "false") << ">";
         else if(k.variant == 15 || k.variant == 16)
-            o << "launch_colstream_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ">";
+            // single precision runs one column per thread (measured: 1024-point columns 83-84 % of the copy rate
+            // against 77-82 % for two packed columns per thread with half the threads)
+            o << "launch_colstream_kernel<" << k.cfg << ", " << (k.variant == 16 ? "true" : "false") << ", "
+              << (k.prec == 0 ? "true" : "false") << ">";
         else if(k.variant == 17 || k.variant == 18)
             o << (k.push ? "launch_colpush_kernel<" : "launch_colcluster_kernel<") << k.cfg << ", 2, "
               << (k.variant == 18 ? "true" : "false") << ">";
@@ -675,7 +679,7 @@ int main(int argc, char** argv)
             o << "    {" << k.n << ", " << k.prec << ", " << k.variant << ", " << k.tpt << ", "
               << (k.pairs ? 2 * k.tpb : k.tpb) << ", "
               << ((k.variant == 17 || k.variant == 18)   ? k.tpt * 4
-                  : (k.variant == 15 || k.variant == 16) ? k.tpt * 8
+                  : (k.variant == 15 || k.variant == 16) ? k.tpt * (k.prec == 0 ? 16 : 8)
                   : (k.variant == 13 || k.variant == 14) ? k.tpt * k.tpb / 2
                                                          : k.tpt * k.tpb)
               << ", " << k.f.size()

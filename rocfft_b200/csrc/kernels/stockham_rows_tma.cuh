@@ -484,6 +484,8 @@ namespace b200fft
         if(ntiles > 0x7fffffffull)
             return cudaErrorInvalidConfiguration;
         unsigned long long grid = resident;
+        if(a.iaux[1] > 0 && grid > (unsigned long long)a.iaux[1])
+            grid = (unsigned long long)a.iaux[1]; // the planner wants room left for a concurrent kernel
         if(grid > ntiles)
             grid = ntiles;
         kern<<<(unsigned)grid, C::THREADS, R::SMEM_BYTES, stream>>>(a);

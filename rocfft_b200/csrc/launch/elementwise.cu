@@ -404,6 +404,45 @@ namespace b200fft
     }
 } // namespace b200fft
 
+// ---- buffer hash for the kernelio log layer ----
+// Order-independent 64-bit checksum of a byte range: every 8-byte word is mixed with its index and the
+// results are summed (the reference's kernelio layer hashes each kernel's input and output,
+// library/src/powX.cpp:743-780, 910-956; this serves the same purpose: telling, kernel by kernel, whether
+// two runs saw the same data).
+namespace b200fft
+{
+    __global__ void __launch_bounds__(256) hash_words_kernel(const unsigned long long* p, size_t words, unsigned long long* out)
+    {
+        unsigned long long acc = 0;
+        for(size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x)
+        {
+            unsigned long long v = p[i] ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(i + 1));
+            v ^= v >> 31;
+            v *= 0xBF58476D1CE4E5B9ull;
+            v ^= v >> 29;
+            acc += v;
+        }
+        for(int o = 16; o > 0; o >>= 1)
+            acc += __shfl_down_sync(0xffffffffu, acc, o);
+        if((threadIdx.x & 31) == 0)
+            atomicAdd(out, acc);
+    }
+}
+
+extern "C" cudaError_t b200fft_launch_hash(const void* p, size_t bytes, unsigned long long* out, cudaStream_t stream)
+{
+    const size_t words = bytes / 8;
+    if(cudaMemsetAsync(out, 0, sizeof(unsigned long long), stream) != cudaSuccess)
+        return cudaGetLastError();
+    if(words == 0)
+        return cudaSuccess;
+    size_t blocks = (words + 255) / 256;
+    if(blocks > 148 * 16)
+        blocks = 148 * 16;
+    b200fft::hash_words_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const unsigned long long*>(p), words, out);
+    return cudaGetLastError();
+}
+
 extern "C" cudaError_t
     b200fft_launch_elementwise(int kind, int precision, const b200fft_eargs* a, cudaStream_t stream)
 {

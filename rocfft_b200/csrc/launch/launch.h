@@ -116,6 +116,9 @@ typedef enum b200fft_ew_kind
 
 cudaError_t b200fft_launch_elementwise(int kind, int precision, const b200fft_eargs* a, cudaStream_t stream);
 
+// order-independent 64-bit checksum of `bytes` bytes (8-byte words) into *out (device memory); kernelio log layer
+cudaError_t b200fft_launch_hash(const void* p, size_t bytes, unsigned long long* out, cudaStream_t stream);
+
 // strided box copy between a brick and the full field (launch/brick_copy.cu); elem_bytes 4 / 8 / 16,
 // four extents and element strides per side, fastest dimension first
 cudaError_t b200fft_launch_brick_copy(void*                     dst,

@@ -272,7 +272,11 @@ namespace b200fft
         // ROCFFT_B200_MGPU_NCCL=1 selects the NCCL send/recv exchange instead.
         sp->p2p = getenv("ROCFFT_B200_MGPU_NCCL") == nullptr;
 
-        // chunking for overlap of compute and exchange (NCCL mode only)
+        // Chunking (NCCL mode only): every pass is cut into k chunks so that chunk c+1 computes while chunk c is
+        // on the wire.  The peer-store mode runs whole passes: cutting passes B and C into chunks and running the
+        // row pass C of chunk c on a second stream beside pass B of chunk c+1 was measured on two GPUs (1024^3)
+        // and gained nothing — B + C took 4.48 ms overlapped against 3.03 + 1.32 ms in sequence: pass B keeps
+        // the SMs busy although its stores cross NVLink — so that variant was dropped.
         int k = 4;
         if(const char* env = getenv("ROCFFT_B200_MGPU_CHUNKS"))
             k = std::max(1, atoi(env));
@@ -281,9 +285,10 @@ namespace b200fft
         if(sp->p2p)
             k = 1;
         sp->chunks = k;
+        const int kA = k; // chunks of pass A
 
         const size_t nx = sp->nx, ny = sp->ny, lz = sp->lz, ly = sp->ly;
-        const size_t cz = lz / k, cy = ly / k;
+        const size_t cz = lz / kA, cy = ly / k;
         const size_t slab_elems = nx * ny * lz; // one batch member's slab
         const size_t nb         = sp->nb;
         sp->slab_bytes          = slab_elems * sp->csize;
@@ -367,18 +372,21 @@ namespace b200fft
             }
             // block q of pass A lands in rank q's T at planes z = rank*lz ..., block q of pass B in
             // rank q's staging buffer at part `rank`; both are rank * (slab / P) bytes into the buffer
+            // (pass B chunk c: the staging buffer holds chunk after chunk, and inside a chunk one part per source rank)
             const size_t       part = sp->slab_bytes / P;
-            std::vector<void*> ta(P), tb(P);
+            std::vector<void*> ta(P), tb((size_t)P * k);
             for(int q = 0; q < P; ++q)
             {
                 ta[q] = static_cast<char*>(sp->peer_r[q]) + (size_t)sp->rank * part;
-                tb[q] = static_cast<char*>(sp->peer_r2[q]) + (size_t)sp->rank * part;
+                for(int c = 0; c < k; ++c)
+                    tb[(size_t)c * P + q] = static_cast<char*>(sp->peer_r2[q]) + (size_t)c * (sp->slab_bytes / k)
+                                            + (size_t)sp->rank * (part / k);
             }
             if(cudaMalloc(&sp->tab_a, sizeof(void*) * P) != cudaSuccess
-               || cudaMalloc(&sp->tab_b, sizeof(void*) * P) != cudaSuccess || cudaMalloc(&sp->bar, 64) != cudaSuccess)
+               || cudaMalloc(&sp->tab_b, sizeof(void*) * P * k) != cudaSuccess || cudaMalloc(&sp->bar, 64) != cudaSuccess)
                 throw std::runtime_error("cudaMalloc failed");
             cudaMemcpy(sp->tab_a, ta.data(), sizeof(void*) * P, cudaMemcpyHostToDevice);
-            cudaMemcpy(sp->tab_b, tb.data(), sizeof(void*) * P, cudaMemcpyHostToDevice);
+            cudaMemcpy(sp->tab_b, tb.data(), sizeof(void*) * P * k, cudaMemcpyHostToDevice);
             cudaMemset(sp->bar, 0, 64);
             S.id = R.id = R2.id = BUF_ABS;
             sp->off_s  = 0;
@@ -460,6 +468,7 @@ namespace b200fft
         for(int c = 0; c < k; ++c)
         {
             // ---- pass A: FFT along Y for z-chunk c, slab -> S_c[q][zc][yq][x]
+            if(c < kA)
             {
                 auto    core = new_core();
                 Planner p(*core);
@@ -476,7 +485,7 @@ namespace b200fft
                 s.in             = user_in;
                 s.in.byte_off[0] = c * cz * nx * ny * sp->csize;
                 s.out            = S;
-                s.out.byte_off[0] = sp->off_s + c * chunk_bytes;
+                s.out.byte_off[0] = sp->off_s + c * (sp->slab_bytes / kA);
                 if(sp->p2p)
                     s.out_blk_ptrs = sp->tab_a;
                 s.inverse        = inverse;
@@ -501,7 +510,7 @@ namespace b200fft
                 s.out             = S;
                 s.out.byte_off[0] = sp->off_s + c * chunk_bytes;
                 if(sp->p2p)
-                    s.out_blk_ptrs = sp->tab_b;
+                    s.out_blk_ptrs = sp->tab_b + (size_t)c * P;
                 s.inverse         = inverse;
                 p.emit_c2c_1d(s);
                 sp->passB.push_back(std::move(core));
@@ -633,6 +642,55 @@ namespace b200fft
         return o.str();
     }
 
+    std::string multi_device_plan_graph(const rocfft_plan_t* plan)
+    {
+        std::ostringstream o;
+        o << "digraph plan {\n  rankdir=TB;\n";
+        if(multi_device_kind(plan) == 1)
+        {
+            // gather -> one single-device transform -> scatter; the text description names the copies
+            o << "  gather [label=\"copy input bricks to one device\"];\n  fft [label=\"single-device transform\"];\n"
+                 "  scatter [label=\"copy result to output bricks\"];\n  gather -> fft -> scatter;\n}";
+            return o.str();
+        }
+        auto* sp = static_cast<const SlabPlan*>(plan->mgpu);
+        if(!sp)
+            return "digraph plan {}";
+        auto items = [&](const char* tag, const char* what, const std::vector<std::unique_ptr<PlanCore>>& v) {
+            std::vector<std::string> ids;
+            for(size_t c = 0; c < v.size(); ++c)
+                for(size_t i = 0; i < v[c]->steps.size(); ++i)
+                {
+                    std::string id = std::string(tag) + std::to_string(c) + "_" + std::to_string(i);
+                    o << "  " << id << " [label=\"rank " << sp->rank << ": " << what << " (" << v[c]->steps[i].note << ")\"];\n";
+                    ids.push_back(id);
+                }
+            return ids;
+        };
+        const char* wa = sp->xsplit ? "FFT along X, local" : "FFT along Y, stores into every rank's T";
+        const char* wb = sp->xsplit ? "FFT along Y, stores into every rank's R" : "FFT along Z, stores into every rank's staging buffer";
+        const char* wc = sp->xsplit ? "FFT along Z, local" : "FFT along X, local";
+        std::vector<std::string> a = items("A", wa, sp->passA), b = items("B", wb, sp->passB), c = items("C", wc, sp->passC);
+        o << "  bar0 [shape=box,label=\"barrier (one-word all-reduce over " << sp->P << " ranks)\"];\n"
+          << "  bar1 [shape=box,label=\"barrier (one-word all-reduce over " << sp->P << " ranks)\"];\n";
+        auto chain = [&](const std::vector<std::string>& ids, const std::string& from, const std::string& to) {
+            std::string prev = from;
+            for(const auto& id : ids)
+            {
+                if(!prev.empty())
+                    o << "  " << prev << " -> " << id << ";\n";
+                prev = id;
+            }
+            if(!to.empty() && !prev.empty())
+                o << "  " << prev << " -> " << to << ";\n";
+        };
+        chain(a, "", "bar0");
+        chain(b, "bar0", "bar1");
+        chain(c, "bar1", "");
+        o << "}";
+        return o.str();
+    }
+
     void multi_device_error_flags(const rocfft_plan_t* plan, std::vector<const int*>& out)
     {
         if(multi_device_kind(plan) == 1)
@@ -646,10 +704,8 @@ namespace b200fft
                     out.push_back(c->dev_error);
         // sums of the ranks' failure flags, carried by the two phase barriers
         if(sp->p2p && sp->bar && sp->P > 1)
-        {
-            out.push_back(sp->bar + 8);
-            out.push_back(sp->bar + 9);
-        }
+            for(int i = 0; i < 2; ++i)
+                out.push_back(sp->bar + 8 + i);
     }
 
     rocfft_status execute_multi_device_plan(rocfft_plan_t*                 plan,

@@ -64,6 +64,8 @@ namespace b200fft
     std::string   describe_multi_device_plan(const rocfft_plan_t* plan);
     // device error flags (PlanCore::dev_error) of every local pass of the plan; null entries skipped
     void          multi_device_error_flags(const rocfft_plan_t* plan, std::vector<const int*>& out);
+    // the plan's items (local FFT passes, barriers, copies) and their order as a graphviz digraph: graph log layer
+    std::string   multi_device_plan_graph(const rocfft_plan_t* plan);
     rocfft_status execute_multi_device_plan(rocfft_plan_t*                 plan,
                                             void* const*                   in,
                                             void* const*                   out,

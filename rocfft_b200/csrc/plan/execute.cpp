@@ -62,7 +62,9 @@ namespace b200fft
                                    void* const*             out,
                                    void*                    work,
                                    cudaStream_t             stream,
-                                   cudaEvent_t*             step_events)
+                                   cudaEvent_t*             step_events,
+                                   StepObserver             observer     = nullptr,
+                                   void*                    observer_ctx = nullptr)
     {
         size_t step_index = 0;
         for(const Step& s : steps)
@@ -80,6 +82,8 @@ namespace b200fft
                 rocfft_status st = run_steps(core, s.alt, in, out, work, stream, nullptr);
                 if(st != rocfft_status_success)
                     return st;
+                if(observer)
+                    observer(observer_ctx, step_index - 1, s, op[0], stream);
                 continue;
             }
 
@@ -140,6 +144,8 @@ namespace b200fft
                 if(k == idx.size())
                     break;
             }
+            if(observer)
+                observer(observer_ctx, step_index - 1, s, op[0], stream);
         }
         if(step_events)
             cudaEventRecord(step_events[step_index], stream);
@@ -151,10 +157,12 @@ namespace b200fft
                                void* const*    out,
                                void*           work,
                                cudaStream_t    stream,
-                               cudaEvent_t*    step_events)
+                               cudaEvent_t*    step_events,
+                               StepObserver    observer,
+                               void*           observer_ctx)
     {
         if(core.host_only)
             return rocfft_status_failure; // no CPU fallback exists
-        return run_steps(core, core.steps, in, out, work, stream, step_events);
+        return run_steps(core, core.steps, in, out, work, stream, step_events, observer, observer_ctx);
     }
 }

@@ -161,12 +161,16 @@ namespace b200fft
     // builds plan->core from the normalised description; throws std::runtime_error
     void build_single_device_plan(rocfft_plan_t* plan);
     // runs every step of `core` on `stream`
+    // called after every top-level step has been enqueued, with the step's resolved output pointer (kernelio log layer)
+    typedef void (*StepObserver)(void* ctx, size_t index, const Step& step, void* out_ptr, cudaStream_t stream);
     rocfft_status execute_core(const PlanCore& core,
                                void* const*    in,
                                void* const*    out,
                                void*           work,
                                cudaStream_t    stream,
-                               cudaEvent_t*    step_events = nullptr); // steps+1 events when profiling
+                               cudaEvent_t*    step_events = nullptr, // steps+1 events when profiling
+                               StepObserver    observer    = nullptr,
+                               void*           observer_ctx = nullptr);
     std::string describe_core(const PlanCore& core);
     extern std::atomic<unsigned long long> g_launch_count; // kernels launched by this library
 

@@ -43,6 +43,9 @@ namespace b200fft
             // second kernel of a long 1D transform: multiply the input by W^(k1 * e), k1 = index of outer[0]
             const void* lt_tab   = nullptr;
             int         lt_steps = 0;
+            // persistent row kernels: upper bound on the number of CTAs (0 = as many as fit the device), for
+            // passes that are meant to share the GPU with another kernel
+            int max_ctas = 0;
         };
 
         inline const b200fft_pool_entry* pool_find(size_t n, int prec, int variant)
@@ -634,6 +637,7 @@ namespace b200fft
                 a.aux[0]    = s.aux0 ? s.aux0 : a.aux[0];
                 a.aux[1]    = s.aux1;
                 a.iaux[0]   = s.iaux0;
+                a.iaux[1]   = s.max_ctas;
                 a.aux[2]    = s.lt_tab;
                 a.iaux[2]   = s.lt_steps;
                 st.ntiles   = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];

@@ -24,14 +24,19 @@ def _rel(a, b):
     return np.linalg.norm(a - b) / np.linalg.norm(b)
 
 
-@pytest.mark.parametrize("lengths,batch", [([256], 1), ([1024], 64), ([64, 64, 64], 1), ([1 << 17], 2)],
-                         ids=["256", "1024x64_rows", "64cubed", "131072_two_kernels"])
-def test_execute_is_capturable_and_replayable(lengths, batch):
+@pytest.mark.parametrize("lengths,batch", [([256], 1), ([1024], 64), ([64, 64, 64], 1), ([1 << 17], 2), ([64, 1024], 2),
+                                           ([1024, 1024], 4)],
+                         ids=["256", "1024x64_rows", "64cubed", "131072_two_kernels", "1024_columns_tensor_copy",
+                              "1024x1024x4_rows_and_columns_in_one_kernel"])
+def test_execute_is_capturable_and_replayable(lengths, batch, monkeypatch):
     """Forward out of place, inverse in place and element-wise work on the same stream are captured
     into one graph; nothing runs before the graph is launched; ten launches give the input back and
     count to ten."""
     import torch
     assert rf.rocfft_setup() == 0
+    if lengths == [1024, 1024]:
+        # the one-kernel path (cooperative launch, counters reset by a memset node); opt-in in single precision
+        monkeypatch.setenv("ROCFFT_B200_2D_L2", "1")
     n = int(np.prod(lengths))
     shape = (batch,) + tuple(reversed(lengths))
     host = _rand(shape, 100)
@@ -40,6 +45,10 @@ def test_execute_is_capturable_and_replayable(lengths, batch):
     counter = torch.zeros(16, dtype=torch.int64, device="cuda")
     fwd = rf.Plan(OOP, FWD, 0, lengths, batch)
     inv = rf.Plan(IP, INV, 0, lengths, batch)
+    if lengths == [1024, 1024]:
+        assert "fft2d_l2" in fwd.describe()
+    if lengths == [64, 1024]:
+        assert "col_tma" in fwd.describe()
     works = []
     for p in (fwd, inv):
         if p.work_bytes:  # capture-friendly: the caller owns the work buffer
