@@ -418,12 +418,14 @@ class SampledCheck3D:
         """out_slab: this rank's output, device tensor viewable as (lz, ny, nx) complex64.  Collective when dist is given."""
         import scipy.fft as sfft
         planes, s_all = self.planes, self.s
+        # collectives run where the process group's backend wants its tensors (NCCL: the GPU; gloo: the host)
+        dev = "cuda" if (dist is not None and dist.get_backend() == "nccl") else "cpu"
         if dist is not None and self.world > 1:
-            t = torch.from_numpy(planes.view(np.float64)).cuda()
+            t = torch.from_numpy(planes.view(np.float64).copy()).to(dev)
             dist.all_reduce(t)
             planes = t.cpu().numpy().view(np.complex128)
-            parts = [torch.empty(self.s.size * 2, dtype=torch.float64, device="cuda") for _ in range(self.world)]
-            dist.all_gather(parts, torch.from_numpy(self.s.view(np.float64).ravel().copy()).cuda())
+            parts = [torch.empty(self.s.size * 2, dtype=torch.float64, device=dev) for _ in range(self.world)]
+            dist.all_gather(parts, torch.from_numpy(self.s.view(np.float64).ravel().copy()).to(dev))
             s_all = np.concatenate([p.cpu().numpy().view(np.complex128).reshape(self.lz, -1) for p in parts], axis=0)
         out = out_slab.view(self.lz, self.ny, self.nx)
         nr = _Norms()
@@ -439,8 +441,8 @@ class SampledCheck3D:
             nsampled += self.lz
         vec = nr.vector()
         if dist is not None and self.world > 1:
-            mx = torch.tensor([vec[0], vec[1]], dtype=torch.float64, device="cuda")
-            sm = torch.tensor([vec[2], vec[3], float(nsampled)], dtype=torch.float64, device="cuda")
+            mx = torch.tensor([vec[0], vec[1]], dtype=torch.float64, device=dev)
+            sm = torch.tensor([vec[2], vec[3], float(nsampled)], dtype=torch.float64, device=dev)
             dist.all_reduce(mx, op=dist.ReduceOp.MAX)
             dist.all_reduce(sm)
             vec = [float(mx[0]), float(mx[1]), float(sm[0]), float(sm[1])]

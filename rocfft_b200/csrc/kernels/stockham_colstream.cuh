@@ -205,10 +205,6 @@ namespace b200fft
         }
     };
 
-#ifdef B200FFT_CS_TIMING
-    __device__ long long g_cs_tm[4]; // harness only: clocks of CTA 0's thread 0 in pass 0 / exchange / pass 1 / store
-    __shared__ long long s_cs_tm[4];
-#endif
     template <class CC, int P, class TWP>
     __device__ __forceinline__ void colstream_compute(typename CC::C2 (&r)[CC::EPT], const TWP* __restrict__ tw, const int tl)
     {
@@ -291,15 +287,7 @@ namespace b200fft
         using PP = ColWidePass<C, P>;
         using T2 = typename C::T2;
         using U  = typename CC::U;
-#ifdef B200FFT_CS_TIMING
-        const long long q0 = clock64();
-#endif
         colstream_compute<CC, P, TWP>(r, tw, tl);
-#ifdef B200FFT_CS_TIMING
-        if(threadIdx.x == 0)
-            g_cs_tm[P == 0 ? 0 : 2] += clock64() - q0;
-        const long long q1 = clock64();
-#endif
         if constexpr(P == C::NPASS - 1)
         {
 #pragma unroll
@@ -317,18 +305,10 @@ namespace b200fft
                     *reinterpret_cast<U*>(dst) = CC::SV::pack(r[i * PP::W + j], sx, sy);
                 }
             }
-#ifdef B200FFT_CS_TIMING
-            if(threadIdx.x == 0)
-                s_cs_tm[3] += clock64() - q1;
-#endif
         }
         else
         {
             colstream_exchange<CC, P>(r, xs, tl, u, P == 0);
-#ifdef B200FFT_CS_TIMING
-            if(threadIdx.x == 0)
-                s_cs_tm[1] += clock64() - q1;
-#endif
             colstream_from<CC, P + 1, BLK, TWP>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
         }
     }
@@ -403,21 +383,10 @@ namespace b200fft
             issue_load(first);
 
         unsigned phase = 0;
-#ifdef B200FFT_CS_TIMING
-        long long tm_wait = 0, tm_a = 0, tm_rest = 0, tm0 = clock64();
-        if(tid == 0)
-            s_cs_tm[0] = s_cs_tm[1] = s_cs_tm[2] = s_cs_tm[3] = 0;
-#endif
         for(unsigned long long tile = first; tile < ntiles; tile += stride)
         {
-#ifdef B200FFT_CS_TIMING
-            const long long c0 = clock64();
-#endif
             const bool landed = ptx::mbar_wait(full, phase);
             phase ^= 1u;
-#ifdef B200FFT_CS_TIMING
-            const long long c1 = clock64();
-#endif
             C2 r[CC::EPT];
             if(landed)
             {
@@ -446,9 +415,6 @@ namespace b200fft
             const unsigned long long next = tile + stride;
             if(tid == 0 && next < ntiles)
                 issue_load(next);
-#ifdef B200FFT_CS_TIMING
-            const long long c2 = clock64();
-#endif
 
             const TilePos   tp    = decode_tile(a, (unsigned)tile, CC::COLS);
             const long long obase = view_base(a.out, tp.i0_first + u * CC::VEC, tp.i1, tp.i2);
@@ -457,26 +423,7 @@ namespace b200fft
                 colstream_from<CC, 0, BLK>(r, xs, tws, tl, u, a, gout, obase, sx, sy);
             else
                 colstream_from<CC, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
-#ifdef B200FFT_CS_TIMING
-            const long long c3 = clock64();
-            tm_wait += c1 - c0;
-            tm_a += c2 - c1;
-            tm_rest += c3 - c2;
-#endif
         }
-#ifdef B200FFT_CS_TIMING
-        if(tid == 0 && a.aux[2])
-        {
-            long long* o = reinterpret_cast<long long*>(const_cast<void*>(a.aux[2])) + 4 * blockIdx.x;
-            o[0] = tm_wait;
-            o[1] = tm_a;
-            o[2] = tm_rest;
-            o[3] = clock64() - tm0;
-            if(blockIdx.x == 1)
-                for(int i = 0; i < 4; ++i)
-                    g_cs_tm[i] = s_cs_tm[i];
-        }
-#endif
     }
 
     // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the library does not link libcuda)

@@ -411,7 +411,7 @@ namespace b200fft
 // two runs saw the same data).
 namespace b200fft
 {
-    __global__ void __launch_bounds__(256) hash_words_kernel(const unsigned long long* p, size_t words, unsigned long long* out)
+    static __global__ void __launch_bounds__(256) hash_words_kernel(const unsigned long long* p, size_t words, unsigned long long* out)
     {
         unsigned long long acc = 0;
         for(size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x)
