@@ -87,6 +87,14 @@ ROCFFT_EXPORT rocfft_status b200fft_slab_exchange_offsets(int     ranks,
                                                           size_t* recv_off,
                                                           size_t* block_bytes);
 
+/* The same for a rank-2 transform on row slabs (rank q holds rows [q*ny/ranks, (q+1)*ny/ranks) of
+ * every image): byte offsets at which rank `rank` stores into EVERY peer's receive buffers — in the
+ * first phase its rows of the peer's T[y][x_local] (x_local = the peer's nx/ranks columns), in the
+ * second its columns of the peer's row buffer [y_local][x].  Called by the plan builder; exported
+ * for the same reason (reference counterpart as above). */
+ROCFFT_EXPORT rocfft_status b200fft_rows2d_exchange_offsets(
+    int ranks, int rank, size_t nx, size_t ny, size_t elem_bytes, size_t* first_off, size_t* second_off);
+
 /* Number of GPU kernels this library has launched in the calling process. */
 ROCFFT_EXPORT unsigned long long b200fft_launch_count();
 

@@ -871,6 +871,15 @@ ROCFFT_EXPORT rocfft_status b200fft_slab_exchange_offsets(int     ranks,
     return rocfft_status_success;
 }
 
+ROCFFT_EXPORT rocfft_status b200fft_rows2d_exchange_offsets(
+    int ranks, int rank, size_t nx, size_t ny, size_t elem_bytes, size_t* first_off, size_t* second_off)
+{
+    if(ranks < 1 || rank < 0 || rank >= ranks || !first_off || !second_off || nx % (size_t)ranks || ny % (size_t)ranks)
+        return rocfft_status_invalid_arg_value;
+    b200fft::rows2d_exchange_offsets(ranks, rank, nx, ny, elem_bytes, first_off, second_off);
+    return rocfft_status_success;
+}
+
 ROCFFT_EXPORT rocfft_status b200fft_nccl_unique_id(void* id128)
 {
     return b200fft::nccl_unique_id(id128) == 0 ? rocfft_status_success : rocfft_status_failure;

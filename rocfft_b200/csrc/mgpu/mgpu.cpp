@@ -28,6 +28,10 @@
 //     rank's buffer over NVLink while they compute (plain peer stores: no multimem, no
 //     TMA).  A one-word NCCL all-reduce on the caller's stream is the barrier between
 //     phases.  The plan then needs no caller work buffer.
+//   * Rank-2 transforms on row slabs use the same machinery with one transform less: the
+//     first phase is a strided copy of every row's x-ranges into the owning ranks'
+//     T[y][x_local], the second the FFT along Y with its store split over the ranks'
+//     row buffers (natural order), the third the FFT along X.
 //   * ROCFFT_B200_MGPU_NCCL=1 selects NCCL grouped send/recv instead: the work is
 //     cut into chunks; chunk c+1 is transformed while chunk c is on the wire (compute
 //     on the caller's stream, NCCL on an internal stream, events in between).
@@ -116,6 +120,11 @@ namespace b200fft
             // straight into the peers' R (one launch per destination), passC = Z columns from R to the caller.
             bool  xsplit = false;
             void* S      = nullptr;
+            // Rank-2 transforms on row slabs (rank q holds rows y in [q*ly, (q+1)*ly) of every image, in and
+            // out): passA = the rows' x-ranges copied straight into the owning ranks' R, which then hold
+            // T[y][x_local]; passB = Y columns of T, stored into the peers' R2 in the natural order
+            // [y_local][x]; passC = X rows from R2 to the caller.
+            bool rows2d = false;
         };
 
         size_t total_work(const SlabPlan& sp)
@@ -155,6 +164,13 @@ namespace b200fft
         }
     }
 
+    void rows2d_exchange_offsets(int ranks, int rank, size_t nx, size_t ny, size_t elem_bytes, size_t* first_off, size_t* second_off)
+    {
+        const size_t lx = nx / (size_t)ranks, ly = ny / (size_t)ranks;
+        *first_off      = (size_t)rank * ly * lx * elem_bytes; // rows y = rank*ly ... of T[y][x_local]
+        *second_off     = (size_t)rank * lx * elem_bytes; // columns x = rank*lx ... of every row of [y_local][x]
+    }
+
     void build_multi_device_plan(rocfft_plan_t* plan)
     {
         const auto& d = plan->desc;
@@ -188,9 +204,41 @@ namespace b200fft
         // ranks must take the same branch, so they agree on it first.
         const bool c2c = plan->transformType == rocfft_transform_type_complex_forward
                          || plan->transformType == rocfft_transform_type_complex_inverse;
-        bool slab_ok = c2c && d.inArrayType == rocfft_array_type_complex_interleaved
-                       && d.outArrayType == rocfft_array_type_complex_interleaved && plan->rank == 3 && plan->batch >= 1
-                       && plan->lengths == plan->userLengths;
+        const bool il_c2c = c2c && d.inArrayType == rocfft_array_type_complex_interleaved
+                            && d.outArrayType == rocfft_array_type_complex_interleaved && plan->batch >= 1
+                            && plan->lengths == plan->userLengths;
+        bool slab_ok = il_c2c && plan->rank == 3;
+        // rank 2: row slabs in and out, peer-store exchange only, column length one kernel can take
+        bool rows_ok = il_c2c && plan->rank == 2 && !getenv("ROCFFT_B200_MGPU_NCCL") && !getenv("ROCFFT_B200_MGPU_NO_ROWS2D");
+        if(rows_ok)
+        {
+            sp->nx = plan->lengths[0];
+            sp->ny = plan->lengths[1];
+            sp->nz = 1;
+            sp->nb = plan->batch;
+            const int prec2 = plan->precision == rocfft_precision_single ? 0 : 1;
+            rows_ok = sp->ny % P == 0 && sp->nx % P == 0 && detail::pool_find(sp->ny, prec2, B200FFT_COL_BLK) != nullptr;
+        }
+        if(rows_ok)
+        {
+            sp->ly = sp->ny / P;
+            sp->lz = 1;
+            auto is_rows = [&](const rocfft_field_t& f) {
+                if(f.bricks.size() != 1)
+                    return false;
+                const rocfft_brick_t& b = f.bricks[0];
+                if(b.lower.size() != 3 || b.upper.size() != 3 || b.stride.size() != 3)
+                    return false;
+                const size_t lo[3] = {0, sp->rank * sp->ly, 0};
+                const size_t hi[3] = {sp->nx, (sp->rank + 1) * sp->ly, sp->nb};
+                const size_t st[3] = {1, sp->nx, sp->nx * sp->ly};
+                for(int i = 0; i < 3; ++i)
+                    if(b.lower[i] != lo[i] || b.upper[i] != hi[i] || ((i < 2 || sp->nb > 1) && b.stride[i] != st[i]))
+                        return false;
+                return true;
+            };
+            rows_ok = is_rows(d.inFields[0]) && is_rows(d.outFields[0]);
+        }
         // the NCCL send/recv exchange moves one transform's slab; batches use the peer-store exchange
         if(plan->batch > 1 && getenv("ROCFFT_B200_MGPU_NCCL"))
             slab_ok = false;
@@ -243,8 +291,12 @@ namespace b200fft
             slab_ok    = in_slab && (sp->xsplit || out_slab);
         }
         {
-            // 0: not a slab layout, 1: slabs in and out, 2: slabs in, X-split out; every rank must say the same
-            int  mine = slab_ok ? (sp->xsplit ? 2 : 1) : 0;
+            // 0: not a slab layout, 1: slabs in and out, 2: slabs in, X-split out, 3: row slabs of a rank-2
+            // transform; every rank must say the same
+            if(rows_ok)
+                slab_ok = true;
+            sp->rows2d = rows_ok;
+            int  mine = slab_ok ? (rows_ok ? 3 : (sp->xsplit ? 2 : 1)) : 0;
             int* dbuf = nullptr;
             if(cudaMalloc(&dbuf, sizeof(int) * (P + 1)) != cudaSuccess)
                 throw std::runtime_error("cudaMalloc failed");
@@ -289,7 +341,7 @@ namespace b200fft
 
         const size_t nx = sp->nx, ny = sp->ny, lz = sp->lz, ly = sp->ly;
         const size_t cz = lz / kA, cy = ly / k;
-        const size_t slab_elems = nx * ny * lz; // one batch member's slab
+        const size_t slab_elems = sp->rows2d ? nx * ly : nx * ny * lz; // one batch member's slab
         const size_t nb         = sp->nb;
         sp->slab_bytes          = slab_elems * sp->csize;
         const int  prec         = plan->precision == rocfft_precision_single ? 0 : 1;
@@ -323,8 +375,8 @@ namespace b200fft
             if(cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
                 sp->p2p = false; // no GPU in this process: the plan stays inspectable only
         }
-        if(sp->xsplit && !sp->p2p)
-            throw std::runtime_error("the single-transpose plan needs a GPU and the peer-store exchange");
+        if((sp->xsplit || sp->rows2d) && !sp->p2p)
+            throw std::runtime_error("this plan needs a GPU and the peer-store exchange");
         if(sp->xsplit && cudaMalloc(&sp->S, sp->slab_bytes * nb) != cudaSuccess)
             throw std::runtime_error("intermediate array allocation failed");
         if(sp->p2p)
@@ -381,6 +433,13 @@ namespace b200fft
                 for(int c = 0; c < k; ++c)
                     tb[(size_t)c * P + q] = static_cast<char*>(sp->peer_r2[q]) + (size_t)c * (sp->slab_bytes / k)
                                             + (size_t)sp->rank * (part / k);
+                // row slabs: this rank's columns x in [rank*lx, (rank+1)*lx) of every row of rank q's [y_local][x]
+                if(sp->rows2d)
+                {
+                    size_t o1 = 0, o2 = 0;
+                    rows2d_exchange_offsets(P, sp->rank, sp->nx, sp->ny, sp->csize, &o1, &o2);
+                    tb[q] = static_cast<char*>(sp->peer_r2[q]) + o2;
+                }
             }
             if(cudaMalloc(&sp->tab_a, sizeof(void*) * P) != cudaSuccess
                || cudaMalloc(&sp->tab_b, sizeof(void*) * P * k) != cudaSuccess || cudaMalloc(&sp->bar, 64) != cudaSuccess)
@@ -395,7 +454,78 @@ namespace b200fft
             sp->work_bytes = 0;
         }
 
-        if(sp->xsplit)
+        if(sp->rows2d)
+        {
+            const size_t lx = nx / P;
+            BufRef       Rb, R2b;
+            Rb.id = R2b.id  = BUF_ABS;
+            Rb.byte_off[0]  = reinterpret_cast<size_t>(sp->R);
+            R2b.byte_off[0] = reinterpret_cast<size_t>(sp->R2);
+            // pass A: no arithmetic.  The x-range of rank q goes from the caller's rows into rank q's
+            // R = T[b][y][x_local] at rows y = rank*ly ...: one strided copy per destination, plain peer stores
+            {
+                auto    core = new_core();
+                Planner p(*core);
+                for(int q = 0; q < P; ++q)
+                {
+                    Stage s;
+                    s.n  = 1;
+                    s.is = s.os = 1;
+                    s.outer.push_back({lx, 1, 1});
+                    s.outer.push_back({ly, (ptrdiff_t)nx, (ptrdiff_t)lx});
+                    s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)(ny * lx)});
+                    s.in              = user_in;
+                    s.in.byte_off[0]  = (size_t)q * lx * sp->csize;
+                    s.out             = Rb;
+                    size_t o1 = 0, o2 = 0;
+                    rows2d_exchange_offsets(P, sp->rank, nx, ny, sp->csize, &o1, &o2);
+                    s.out.byte_off[0] = reinterpret_cast<size_t>(sp->peer_r[q]) + o1;
+                    p.emit_c2c_1d(s);
+                }
+                sp->passA.push_back(std::move(core));
+            }
+            // pass B: FFT along Y on T; output point y belongs to rank y / ly, whose R2 is laid out like the
+            // caller's slab, [b][y_local][x]: the store splits Y into per-destination blocks
+            {
+                auto    core = new_core();
+                Planner p(*core);
+                Stage   s;
+                s.n       = ny;
+                s.is      = (ptrdiff_t)lx;
+                s.os      = (ptrdiff_t)nx;
+                s.out_blk = ly;
+                s.out_bs  = 0;
+                s.outer.push_back({lx, 1, 1});
+                s.outer.push_back({nb, (ptrdiff_t)(ny * lx), (ptrdiff_t)slab_elems});
+                s.in           = Rb;
+                s.out          = R2b;
+                s.out_blk_ptrs = sp->tab_b;
+                s.inverse      = inverse;
+                p.emit_c2c_1d(s);
+                sp->passB.push_back(std::move(core));
+            }
+            // pass C: FFT along X, R2 -> the caller's slab
+            {
+                auto    core = new_core();
+                Planner p(*core);
+                Stage   s;
+                s.n  = nx;
+                s.is = s.os = 1;
+                s.outer.push_back({ly, (ptrdiff_t)nx, (ptrdiff_t)nx});
+                s.outer.push_back({nb, (ptrdiff_t)slab_elems, (ptrdiff_t)slab_elems});
+                s.in      = R2b;
+                s.out     = user_out;
+                s.inverse = inverse;
+                if(d.scale != 1.0)
+                {
+                    s.use_scale = true;
+                    s.scale     = d.scale;
+                }
+                p.emit_c2c_1d(s);
+                sp->passC.push_back(std::move(core));
+            }
+        }
+        else if(sp->xsplit)
         {
             const size_t lx = nx / P;
             BufRef       Sb, Rb;
@@ -632,12 +762,14 @@ namespace b200fft
         std::ostringstream o;
         o << "slab plan: ranks " << sp->P << " rank " << sp->rank << " lengths " << sp->nx << "x" << sp->ny << "x"
           << sp->nz << " batch " << sp->nb << (sp->xsplit ? " output split along x (one global transpose)" : "")
+          << (sp->rows2d ? " row slabs of a rank-2 transform" : "")
           << " chunks " << sp->chunks << " work bytes " << sp->work_bytes << "\n";
         for(int c = 0; c < sp->chunks; ++c)
         {
-            o << "chunk " << c << " pass A (Y):\n" << describe_core(*sp->passA[c]);
-            o << "chunk " << c << " pass B (Z):\n" << describe_core(*sp->passB[c]);
-            o << "chunk " << c << " pass C (X):\n" << describe_core(*sp->passC[c]);
+            o << "chunk " << c << (sp->rows2d ? " pass A (copy):\n" : sp->xsplit ? " pass A (X):\n" : " pass A (Y):\n")
+              << describe_core(*sp->passA[c]);
+            o << "chunk " << c << (sp->rows2d || sp->xsplit ? " pass B (Y):\n" : " pass B (Z):\n") << describe_core(*sp->passB[c]);
+            o << "chunk " << c << (sp->xsplit ? " pass C (Z):\n" : " pass C (X):\n") << describe_core(*sp->passC[c]);
         }
         return o.str();
     }
@@ -667,9 +799,13 @@ namespace b200fft
                 }
             return ids;
         };
-        const char* wa = sp->xsplit ? "FFT along X, local" : "FFT along Y, stores into every rank's T";
-        const char* wb = sp->xsplit ? "FFT along Y, stores into every rank's R" : "FFT along Z, stores into every rank's staging buffer";
-        const char* wc = sp->xsplit ? "FFT along Z, local" : "FFT along X, local";
+        const char* wa = sp->rows2d   ? "copy of the rows' x-ranges into every rank's T"
+                         : sp->xsplit ? "FFT along X, local"
+                                      : "FFT along Y, stores into every rank's T";
+        const char* wb = sp->rows2d   ? "FFT along Y, stores into every rank's row buffer"
+                         : sp->xsplit ? "FFT along Y, stores into every rank's R"
+                                      : "FFT along Z, stores into every rank's staging buffer";
+        const char* wc = sp->rows2d ? "FFT along X, local" : sp->xsplit ? "FFT along Z, local" : "FFT along X, local";
         std::vector<std::string> a = items("A", wa, sp->passA), b = items("B", wb, sp->passB), c = items("C", wc, sp->passC);
         o << "  bar0 [shape=box,label=\"barrier (one-word all-reduce over " << sp->P << " ranks)\"];\n"
           << "  bar1 [shape=box,label=\"barrier (one-word all-reduce over " << sp->P << " ranks)\"];\n";

@@ -81,6 +81,10 @@ namespace b200fft
                                size_t* recv_off,
                                size_t* block_bytes);
 
+    // where rank `rank` of `ranks` stores into every peer's buffers in a row-slab rank-2 plan (byte offsets):
+    // first phase: its rows of the peer's T[y][x_local]; second phase: its columns of the peer's [y_local][x]
+    void rows2d_exchange_offsets(int ranks, int rank, size_t nx, size_t ny, size_t elem_bytes, size_t* first_off, size_t* second_off);
+
     // NCCL communicator helpers (0 on success)
     int nccl_unique_id(void* out128);
     int nccl_comm_create(int nranks, int rank, const void* id128, void** comm_out);

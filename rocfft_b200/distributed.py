@@ -60,32 +60,40 @@ def create_nccl_comm(dist):
 
 class SlabFFT3D:
     """3D complex transform of lengths (nx, ny, nz) [nx fastest] whose data is
-    split into contiguous Z-slabs, one per rank, in place or out of place.  With
+    split into contiguous Z-slabs, one per rank, in place or out of place (two
+    lengths (nx, ny): a 2D transform split into row slabs, rank q holding rows
+    ``[q*ny/world, (q+1)*ny/world)`` of every image on both sides).  With
     ``out_split="x"`` the result is left split along X instead (rank q holds
     ``[batch][nz][ny][nx/world]``): one global transpose instead of two, the
     reference's "slow in, fast out" layout (clients/tests/multi_device_test.cpp:117-123)."""
 
     def __init__(self, comm, rank, world, lengths, precision=rf.rocfft_precision_single, inverse=False,
                  inplace=True, scale=None, batch=1, out_split="z"):
-        nx, ny, nz = lengths
-        assert nz % world == 0 and ny % world == 0
-        assert out_split in ("z", "x") and (out_split == "z" or nx % world == 0)
-        self.lz = nz // world
+        lengths = list(lengths)
         self.comm = comm
         self._comm_box = ctypes.c_void_p(comm.value)
         st, self.desc = rf.rocfft_plan_description_create()
         assert st == 0
         st = rf.rocfft_plan_description_set_comm(self.desc, rf.rocfft_comm_nccl, ctypes.byref(self._comm_box))
         assert st == 0, st
-        lower = [0, 0, rank * self.lz, 0]
-        upper = [nx, ny, (rank + 1) * self.lz, batch]
-        stride = [1, nx, nx * ny, nx * ny * self.lz]
-        lx = nx // world
-        for adder in (rf.rocfft_plan_description_add_infield, rf.rocfft_plan_description_add_outfield):
+        if len(lengths) == 2:
+            # rank-2 transform: rank q holds the rows y in [q*ly, (q+1)*ly) of every image, in and out
+            nx, ny = lengths
+            assert ny % world == 0 and nx % world == 0 and out_split == "z"
+            ly = ny // world
+            bricks = [([0, rank * ly, 0], [nx, (rank + 1) * ly, batch], [1, nx, nx * ly])] * 2
+        else:
+            nx, ny, nz = lengths
+            assert nz % world == 0 and ny % world == 0
+            assert out_split in ("z", "x") and (out_split == "z" or nx % world == 0)
+            self.lz = nz // world
+            lx = nx // world
+            zslab = ([0, 0, rank * self.lz, 0], [nx, ny, (rank + 1) * self.lz, batch], [1, nx, nx * ny, nx * ny * self.lz])
+            xsplit = ([rank * lx, 0, 0, 0], [(rank + 1) * lx, ny, nz, batch], [1, lx, lx * ny, lx * ny * nz])
+            bricks = [zslab, xsplit if out_split == "x" else zslab]
+        for adder, (lower, upper, stride) in zip((rf.rocfft_plan_description_add_infield,
+                                                  rf.rocfft_plan_description_add_outfield), bricks):
             st, field = rf.rocfft_field_create()
-            if adder is rf.rocfft_plan_description_add_outfield and out_split == "x":
-                lower, upper = [rank * lx, 0, 0, 0], [(rank + 1) * lx, ny, nz, batch]
-                stride = [1, lx, lx * ny, lx * ny * nz]
             st, brick = rf.rocfft_brick_create(lower, upper, stride, 0 if world == 1 else _current_device())
             assert st == 0
             assert rf.rocfft_field_add_brick(field, brick) == 0
@@ -96,7 +104,7 @@ class SlabFFT3D:
             rf.rocfft_plan_description_set_scale_factor(self.desc, scale)
         tt = rf.rocfft_transform_type_complex_inverse if inverse else rf.rocfft_transform_type_complex_forward
         st, self.plan = rf.rocfft_plan_create(rf.rocfft_placement_inplace if inplace else rf.rocfft_placement_notinplace,
-                                              tt, precision, [nx, ny, nz], batch, self.desc)
+                                              tt, precision, lengths, batch, self.desc)
         if st != 0:
             raise RuntimeError(f"multi-device rocfft_plan_create failed: {st}")
         st, self.work_bytes = rf.rocfft_plan_get_work_buffer_size(self.plan)

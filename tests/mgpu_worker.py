@@ -1,5 +1,5 @@
 """Worker for the multi-GPU tests: one rank per GPU under torch.distributed.run.
-Runs a slab-decomposed 3D transform through the field/brick API and compares
+Runs a slab-decomposed 3D (or, with two lengths, row-slab 2D) transform through the field/brick API and compares
 the gathered result with the CPU oracle on rank 0 (the reference's MPI worker,
 clients/tests/rocfft_mpi_worker.cpp, does the same against FFTW)."""
 import os
@@ -37,7 +37,11 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     assert rf.rocfft_setup() == 0
     comm = D.create_nccl_comm(dist)
-    nx, ny, nz = lengths
+    rows2d = len(lengths) == 2  # rank-2 transform on row slabs: the slab dimension is Y
+    if rows2d:
+        (nx, nz), ny = lengths, 1
+    else:
+        nx, ny, nz = lengths
     lz = nz // world
     cdt = np.complex64 if prec == "single" else np.complex128
     full = orc.uniform_input((batch, nz, ny, nx), cdt, seed=11)
@@ -49,6 +53,8 @@ def main():
                       inverse=inverse, inplace=inplace, scale=0.5, batch=batch, out_split=out_split)
     if world > 1 or batch > 1:
         assert "slab plan" in fft_describe(fft), "the optimised slab plan should serve this layout"
+    if rows2d:
+        assert "row slabs of a rank-2 transform" in fft_describe(fft)
     stream = torch.cuda.Stream()
     fft.attach(torch, stream.cuda_stream)
     for rep in range(2):  # twice: the second run exercises buffer reuse across calls
@@ -66,7 +72,7 @@ def main():
     ok = True
     if rank == 0:
         got = torch.cat(gathered, dim=3 if out_split == "x" else 1).cpu().numpy()
-        ref = orc.c2c(full, +1 if inverse else -1) * 0.5
+        ref = orc.c2c(full.reshape(batch, nz, nx) if rows2d else full, +1 if inverse else -1).reshape(full.shape) * 0.5
         ok, msg = orc.check_accuracy(got, ref, prec, nx * ny * nz)
         print(f"mgpu {lengths} batch {batch} {prec} inverse={inverse} inplace={inplace} world={world}: {msg} -> {'ok' if ok else 'FAIL'}",
               flush=True)

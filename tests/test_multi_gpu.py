@@ -94,3 +94,16 @@ def test_slab_in_x_split_out_single_transpose(gpu, lengths, prec, direction, pla
     """Input split along the slowest dimension, output along the fastest (the reference's SLOW_IN_FAST_OUT,
     clients/tests/multi_device_test.cpp:117-123): the optimised plan then needs one global transpose, not two."""
     _launch(min(2, gpu.cuda.device_count()), lengths, prec, direction, placement, 29634, batch, "x")
+
+
+@pytest.mark.parametrize("lengths,prec,direction,placement,batch", [
+    ("256x256", "single", "fwd", "ip", 4),
+    ("64x128", "double", "inv", "op", 1),
+    ("1024x1024", "single", "fwd", "op", 2),
+])
+def test_row_slab_2d_plan(gpu, lengths, prec, direction, placement, batch):
+    """Rank-2 transforms split into row slabs on both sides (the 2D cases of the reference's multi-device tests,
+    clients/tests/multi_device_test.cpp:100-136, split on the slowest dimension) run through the fused peer-store
+    plan, not gather / scatter: copy into the owners' column blocks, Y transform with the store split over the
+    ranks' row buffers, X transform."""
+    _launch(min(2, gpu.cuda.device_count()), lengths, prec, direction, placement, 29635, batch)

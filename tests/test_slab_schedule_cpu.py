@@ -19,3 +19,12 @@ def test_slab_decomposition_over_gloo(built_library, world, shape, chunks):
            os.path.join(ROOT, "tests", "slab_cpu_worker.py")] + [str(v) for v in shape] + [str(chunks)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("world,nx,ny,batch", [(2, 8, 12, 1), (2, 16, 8, 3), (4, 8, 16, 2)])
+def test_row_slab_2d_decomposition_over_gloo(built_library, world, nx, ny, batch):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29760 + world + batch),
+           os.path.join(ROOT, "tests", "rows2d_cpu_worker.py"), str(nx), str(ny), str(batch)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
