@@ -599,7 +599,7 @@ int main(int argc, char** argv)
             Kernel2D    k;
             k.n0 = k.n1 = n;
             k.prec      = prec;
-            k.threads   = 32 * un;
+            k.threads   = (prec == 0 ? 64 : 32) * un; // one column per thread: 8-byte units in single precision
             k.f0 = k.f1 = {32, 32};
             k.smem      = 256 + (size_t)n * un * 16 + (size_t)(n + (n >> 5) + 1) * un * 8 + 16 + 31 * 32 * 16;
             k.minb      = un == 8 ? 1 : 2;

@@ -37,6 +37,7 @@
 #pragma once
 #include "stockham_colpush.cuh"
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 #include <utility>
 
@@ -56,6 +57,18 @@ namespace b200fft
                          "r"(c2),
                          "r"(c3),
                          "r"(smem_u32(bar))
+                         : "memory");
+        }
+        // 4D tiled box store, shared -> global, tracked by the issuing thread's bulk groups
+        __device__ __forceinline__ void
+            tma_store_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3, const void* smem_src)
+        {
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(map),
+                         "r"(c0),
+                         "r"(c1),
+                         "r"(c2),
+                         "r"(c3),
+                         "r"(smem_u32(smem_src))
                          : "memory");
         }
     }
@@ -198,6 +211,10 @@ namespace b200fft
         static constexpr int      TW_ENTRIES  = TW_SMEM ? (C::FL::get(1) - 1) * C::FL::get(0) : 0;
         static constexpr size_t   TW_BYTES    = (size_t)TW_ENTRIES * sizeof(typename SV::TWS);
         static constexpr size_t   SMEM_BYTES  = 256 + STAGE_BYTES + XCHG_BYTES + 16 + TW_BYTES; // slack to align the stage to 256 bytes
+        // results leave through the exchange buffer, half a tile at a time, as tensor stores
+        static constexpr int      OBOX_ROWS   = C::N / 2 < 256 ? C::N / 2 : 256;
+        static constexpr int      ONBOX       = (C::N / 2) / OBOX_ROWS; // boxes per half tile
+        static_assert(C::NPASS < 2 || XCHG_BYTES >= (size_t)(C::N / 2) * ROW_BYTES, "half a tile must fit the exchange buffer");
         static_assert((C::N & (C::N - 1)) == 0 && C::N >= 32, "power-of-two lengths only");
         __device__ static __forceinline__ int prow(int e)
         {
@@ -313,13 +330,85 @@ namespace b200fft
         }
     }
 
+    // all passes from P on, results of the last pass left in r
+    template <class CC, int P, class TWP>
+    __device__ __forceinline__ void colstream_run(typename CC::C2 (&r)[CC::EPT],
+                                                  typename CC::P* xs,
+                                                  const TWP* __restrict__ tw,
+                                                  const int               tl,
+                                                  const int               u)
+    {
+        using C = typename CC::Cfg;
+        colstream_compute<CC, P, TWP>(r, tw, tl);
+        if constexpr(P < C::NPASS - 1)
+        {
+            colstream_exchange<CC, P>(r, xs, tl, u, P == 0);
+            colstream_run<CC, P + 1, TWP>(r, xs, tw, tl, u);
+        }
+    }
+
+    // Results of the last pass (in r) -> global memory as tensor stores, half a tile at a time through the
+    // exchange buffer `xs` (free once every thread is past its last exchange read).  Thread 0 calls
+    // issue(first row of the box, shared-memory source) for every box and commits them as one bulk group;
+    // it must have waited for the reads of the previous tile's groups before the buffer was last reused.
+    template <class CC, class Issue>
+    __device__ __forceinline__ void colstream_store_staged(typename CC::C2 (&r)[CC::EPT],
+                                                           typename CC::P*      xs,
+                                                           const int            tl,
+                                                           const int            u,
+                                                           const int            tid,
+                                                           const typename CC::T sx,
+                                                           const typename CC::T sy,
+                                                           Issue&&              issue)
+    {
+        using C  = typename CC::Cfg;
+        using U  = typename CC::U;
+        using PL = ColWidePass<C, C::NPASS - 1>;
+        static_assert(PL::W * PL::CH == C::N && PL::W % 2 == 0, "the last pass spans the whole transform");
+        U* ost = reinterpret_cast<U*>(xs);
+#pragma unroll
+        for(int half = 0; half < 2; ++half)
+        {
+            if(half == 1 && tid == 0)
+                ptx::bulk_wait_read<0>(); // the first half has been read out of the buffer
+            // half 0: every thread is past its last read of the exchange buffer
+            __syncthreads();
+#pragma unroll
+            for(int i = 0; i < PL::BPT; ++i)
+            {
+                const int b = tl + i * C::TPT; // < CH: output rows b + j * CH
+#pragma unroll
+                for(int j = half * (PL::W / 2); j < (half + 1) * (PL::W / 2); ++j)
+                    ost[(b + (j - half * (PL::W / 2)) * PL::CH) * CC::UNITS + u] = CC::SV::pack(r[i * PL::W + j], sx, sy);
+            }
+            ptx::fence_async_smem(); // written through the generic proxy, read by the copy engine
+            __syncthreads();
+            if(tid == 0)
+            {
+#pragma unroll
+                for(int bx = 0; bx < CC::ONBOX; ++bx)
+                    issue(half * (C::N / 2) + bx * CC::OBOX_ROWS,
+                          reinterpret_cast<const unsigned char*>(ost) + (size_t)bx * CC::OBOX_ROWS * CC::ROW_BYTES);
+                ptx::bulk_commit();
+            }
+        }
+    }
+
     // kargs as for the other column kernels; aux[3] = device error flag (int*).  `map` describes
     // the input array: dimension 0 = 8-byte elements along the columns, 1 = the transform,
     // 2 / 3 = the outer dimensions on[1] / on[2].
-    template <class C, bool BLK, bool SC = false>
+    //
+    // TS: the results leave as tensor stores (the copy engine writes the strided rows; the warps do not
+    // wait on 1024 scattered lines per tile): each half of the tile goes through the exchange buffer,
+    // which is free after the last pass, and `omap` describes the output array like `map` the input
+    // (its dimension order in bits 8-13 of iaux[3]).  Without TS the threads store from registers.
+    template <class C, bool BLK, bool SC = false, bool TS = false>
     __global__ void __launch_bounds__((ColStream<C, 8, SC>::THREADS), C::MINB)
-        stockham_colstream_kernel(const __grid_constant__ b200fft_kargs a, const __grid_constant__ CUtensorMap map)
+        stockham_colstream_kernel(const __grid_constant__ b200fft_kargs a,
+                                  const __grid_constant__ CUtensorMap   map,
+                                  const __grid_constant__ CUtensorMap   omap)
     {
+        static_assert(!TS || (!BLK && C::NPASS >= 2), "tensor stores: plain output, at least two passes");
         using CC = ColStream<C, 8, SC>;
         using T  = typename C::T;
         using T2 = typename C::T2;
@@ -387,6 +476,9 @@ namespace b200fft
         {
             const bool landed = ptx::mbar_wait(full, phase);
             phase ^= 1u;
+            if constexpr(TS)
+                if(tid == 0)
+                    ptx::bulk_wait_read<0>(); // the previous tile's stores have read the exchange buffer
             C2 r[CC::EPT];
             if(landed)
             {
@@ -408,6 +500,8 @@ namespace b200fft
                     if(err)
                         atomicExch(err, 1);
                     ptx::mbar_wait(full, phase ^ 1u); // the copy may still be in flight: give it one more bounded wait
+                    if constexpr(TS)
+                        ptx::bulk_wait_all(); // our own stores
                 }
                 __syncthreads();
                 return;
@@ -417,13 +511,33 @@ namespace b200fft
                 issue_load(next);
 
             const TilePos   tp    = decode_tile(a, (unsigned)tile, CC::COLS);
-            const long long obase = view_base(a.out, tp.i0_first + u * CC::VEC, tp.i1, tp.i2);
-            T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
-            if constexpr(CC::TW_SMEM)
-                colstream_from<CC, 0, BLK>(r, xs, tws, tl, u, a, gout, obase, sx, sy);
+            if constexpr(TS)
+            {
+                if constexpr(CC::TW_SMEM)
+                    colstream_run<CC, 0>(r, xs, tws, tl, u);
+                else
+                    colstream_run<CC, 0>(r, xs, tw, tl, u);
+                const int oe = (int)((a.iaux[3] >> 8) & 3), o1 = (int)((a.iaux[3] >> 10) & 3);
+                colstream_store_staged<CC>(r, xs, tl, u, tid, sx, sy, [&](int row, const unsigned char* src) {
+                    const int c1 = oe == 0 ? row : (o1 == 0 ? (int)tp.i1 : (int)tp.i2);
+                    const int c2 = oe == 1 ? row : (o1 == 1 ? (int)tp.i1 : (int)tp.i2);
+                    const int c3 = oe == 2 ? row : (o1 == 2 ? (int)tp.i1 : (int)tp.i2);
+                    ptx::tma_store_4d(&omap, (int)(tp.i0_first * (unsigned)(sizeof(T2) / 8)), c1, c2, c3, src);
+                });
+            }
             else
-                colstream_from<CC, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+            {
+                const long long obase = view_base(a.out, tp.i0_first + u * CC::VEC, tp.i1, tp.i2);
+                T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
+                if constexpr(CC::TW_SMEM)
+                    colstream_from<CC, 0, BLK>(r, xs, tws, tl, u, a, gout, obase, sx, sy);
+                else
+                    colstream_from<CC, 0, BLK>(r, xs, tw, tl, u, a, gout, obase, sx, sy);
+            }
         }
+        if constexpr(TS)
+            if(tid == 0)
+                ptx::bulk_wait_all(); // nothing of ours may be in flight when the CTA retires
     }
 
     // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the library does not link libcuda)
@@ -453,55 +567,31 @@ namespace b200fft
         return fn;
     }
 
-    template <class C, bool BLK, bool SC = false>
-    cudaError_t launch_colstream_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
+    // One side of a column stage as a 4D tensor of 8-byte elements: dimension 0 runs along the columns;
+    // the transform dimension and the two outer dimensions follow by ascending stride (unit-length
+    // dimensions last, with a stride that continues the sequence).  `perm` tells the kernel where the
+    // transform (bits 0-1), outer 1 (2-3) and outer 2 (4-5) ended up.  False: the view does not fit a map.
+    inline bool colstream_tile_map(CUtensorMap*          map,
+                                   long long*            perm_out,
+                                   const b200fft_ioview& v,
+                                   const b200fft_kargs&  a,
+                                   unsigned              n,
+                                   size_t                elem_bytes,
+                                   unsigned              box_rows)
     {
-        using CC                      = ColStream<C, 8, SC>;
-        using T2                      = typename C::T2;
-        static int        blocks_per_sm[64] = {};
-        static int        sm_count[64]      = {};
-        static std::mutex mtx;
-        int               dev = 0;
-        cudaGetDevice(&dev);
-        if(dev < 0 || dev >= 64)
-            return cudaErrorInvalidDevice;
-        auto kern = stockham_colstream_kernel<C, BLK, SC>;
-        {
-            std::lock_guard<std::mutex> g(mtx);
-            if(!blocks_per_sm[dev])
-            {
-                cudaError_t e
-                    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CC::SMEM_BYTES);
-                if(e != cudaSuccess)
-                    return e;
-                int nb = 0;
-                e      = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, CC::THREADS, CC::SMEM_BYTES);
-                if(e != cudaSuccess)
-                    return e;
-                cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-                blocks_per_sm[dev] = nb > 0 ? nb : 1;
-            }
-        }
-        if(ntiles == 0)
-            return cudaSuccess;
-        if(ntiles > 0x7fffffffull)
-            return cudaErrorInvalidConfiguration;
         tmap_encode_fn enc = tmap_encoder();
         if(!enc)
-            return cudaErrorNotSupported;
-        // The input array as a 4D tensor of 8-byte elements: dimension 0 runs along the columns; the
-        // transform dimension and the two outer dimensions follow by ascending stride (unit-length
-        // dimensions last, with a stride that continues the sequence).
-        if(a.in.es <= 0 || (a.on[1] > 1 && a.in.os[1] <= 0) || (a.on[2] > 1 && a.in.os[2] <= 0))
-            return cudaErrorInvalidValue;
+            return false;
+        if(v.es <= 0 || (a.on[1] > 1 && v.os[1] <= 0) || (a.on[2] > 1 && v.os[2] <= 0))
+            return false;
         struct Dim
         {
             cuuint64_t len, stride;
             int        which; // 0 transform, 1 outer 1, 2 outer 2
         };
-        Dim d[3] = {{(cuuint64_t)C::N, (cuuint64_t)a.in.es * sizeof(T2), 0},
-                    {a.on[1], (cuuint64_t)a.in.os[1] * sizeof(T2), 1},
-                    {a.on[2], (cuuint64_t)a.in.os[2] * sizeof(T2), 2}};
+        Dim d[3] = {{(cuuint64_t)n, (cuuint64_t)v.es * elem_bytes, 0},
+                    {a.on[1], (cuuint64_t)v.os[1] * elem_bytes, 1},
+                    {a.on[2], (cuuint64_t)v.os[2] * elem_bytes, 2}};
         auto before = [](const Dim& x, const Dim& y) {
             const bool ux = x.len <= 1 && x.which != 0, uy = y.len <= 1 && y.which != 0;
             if(ux != uy)
@@ -518,7 +608,10 @@ namespace b200fft
                 d[i].len    = 1;
                 d[i].stride = d[i - 1].stride * d[i - 1].len;
             }
-        const cuuint64_t ce         = sizeof(T2) / 8;
+        for(int i = 0; i < 3; ++i)
+            if(d[i].stride >= (1ull << 40) || d[i].stride % 16)
+                return false;
+        const cuuint64_t ce         = elem_bytes / 8;
         const cuuint64_t dims[4]    = {(cuuint64_t)a.on[0] * ce, d[0].len, d[1].len, d[2].len};
         const cuuint64_t strides[3] = {d[0].stride, d[1].stride, d[2].stride};
         cuuint32_t       box[4]     = {16, 1, 1, 1};
@@ -526,31 +619,100 @@ namespace b200fft
         for(int i = 0; i < 3; ++i)
         {
             if(d[i].which == 0)
-                box[1 + i] = (cuuint32_t)CC::BOX_ROWS;
+                box[1 + i] = (cuuint32_t)box_rows;
             perm |= (long long)i << (2 * d[i].which);
         }
-        b200fft_kargs ka = a;
-        ka.iaux[3]       = perm;
+        *perm_out                = perm;
         const cuuint32_t estr[4] = {1, 1, 1, 1};
-        alignas(64) CUtensorMap map;
-        if(enc(&map,
-               CU_TENSOR_MAP_DATA_TYPE_UINT64,
-               4,
-               a.in.p[0],
-               dims,
-               strides,
-               box,
-               estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
-           != CUDA_SUCCESS)
+        return enc(map,
+                   CU_TENSOR_MAP_DATA_TYPE_UINT64,
+                   4,
+                   v.p[0],
+                   dims,
+                   strides,
+                   box,
+                   estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+               == CUDA_SUCCESS;
+    }
+
+    template <class C, bool BLK, bool SC, bool TS>
+    cudaError_t colstream_grid(int dev, unsigned long long* grid)
+    {
+        using CC = ColStream<C, 8, SC>;
+        static int        blocks_per_sm[64] = {};
+        static int        sm_count[64]      = {};
+        static std::mutex mtx;
+        auto              kern = stockham_colstream_kernel<C, BLK, SC, TS>;
+        std::lock_guard<std::mutex> g(mtx);
+        if(!blocks_per_sm[dev])
+        {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CC::SMEM_BYTES);
+            if(e != cudaSuccess)
+                return e;
+            int nb = 0;
+            e      = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, CC::THREADS, CC::SMEM_BYTES);
+            if(e != cudaSuccess)
+                return e;
+            cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+            blocks_per_sm[dev] = nb > 0 ? nb : 1;
+        }
+        *grid = (unsigned long long)blocks_per_sm[dev] * sm_count[dev];
+        return cudaSuccess;
+    }
+
+    template <class C, bool BLK, bool SC = false>
+    cudaError_t launch_colstream_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
+    {
+        using CC = ColStream<C, 8, SC>;
+        using T2 = typename C::T2;
+        int dev  = 0;
+        cudaGetDevice(&dev);
+        if(dev < 0 || dev >= 64)
+            return cudaErrorInvalidDevice;
+        // plain output that a tensor map can describe leaves through tensor stores (B200FFT_COLTMA_REG_STORES,
+        // read once, keeps the stores in the threads: measurements)
+        static const bool reg_stores = getenv("B200FFT_COLTMA_REG_STORES") != nullptr;
+        constexpr bool    CAN_TS     = !BLK && C::NPASS >= 2;
+        if(ntiles == 0)
+            return cudaSuccess;
+        if(ntiles > 0x7fffffffull)
+            return cudaErrorInvalidConfiguration;
+        if(!tmap_encoder())
+            return cudaErrorNotSupported;
+        alignas(64) CUtensorMap map, omap;
+        long long               perm = 0, operm = 0;
+        if(!colstream_tile_map(&map, &perm, a.in, a, (unsigned)C::N, sizeof(T2), (unsigned)CC::BOX_ROWS))
             return cudaErrorInvalidValue;
-        unsigned long long grid = (unsigned long long)blocks_per_sm[dev] * sm_count[dev];
+        bool ts = false;
+        if constexpr(CAN_TS)
+            ts = !reg_stores && (reinterpret_cast<size_t>(a.out.p[0]) % 16 == 0)
+                 && colstream_tile_map(&omap, &operm, a.out, a, (unsigned)C::N, sizeof(T2), (unsigned)CC::OBOX_ROWS);
+        if(!ts)
+            omap = map;
+        b200fft_kargs ka = a;
+        ka.iaux[3]       = perm | (operm << 8);
+        unsigned long long grid = 0;
+        if constexpr(CAN_TS)
+            if(ts)
+            {
+                cudaError_t e = colstream_grid<C, BLK, SC, true>(dev, &grid);
+                if(e != cudaSuccess)
+                    return e;
+                if(grid > ntiles)
+                    grid = ntiles;
+                stockham_colstream_kernel<C, BLK, SC, true><<<(unsigned)grid, CC::THREADS, CC::SMEM_BYTES, stream>>>(ka, map, omap);
+                return cudaGetLastError();
+            }
+        cudaError_t e = colstream_grid<C, BLK, SC, false>(dev, &grid);
+        if(e != cudaSuccess)
+            return e;
         if(grid > ntiles)
             grid = ntiles;
-        kern<<<(unsigned)grid, CC::THREADS, CC::SMEM_BYTES, stream>>>(ka, map);
+        stockham_colstream_kernel<C, BLK, SC, false><<<(unsigned)grid, CC::THREADS, CC::SMEM_BYTES, stream>>>(ka, map, omap);
         return cudaGetLastError();
     }
 } // namespace b200fft

@@ -59,7 +59,9 @@ namespace b200fft
     template <class C, int UN>
     struct FusedL2
     {
-        using CC                         = ColStream<C, UN>;
+        // single precision in scalar form (one column per thread, 16 warps per 128-byte-wide tile)
+        static constexpr bool SC         = sizeof(typename C::T) == 4;
+        using CC                         = ColStream<C, UN, SC>;
         using T                          = typename C::T;
         using T2                         = typename C::T2;
         static constexpr int N           = C::N;
@@ -72,6 +74,7 @@ namespace b200fft
         static constexpr size_t SMEM_BYTES = CC::SMEM_BYTES;
         static_assert(C::TPT == 32 && C::NPASS == 2 && CC::EPT == 32, "two radix-32-wide passes, one butterfly per lane");
         static_assert((unsigned)ROWS * N * sizeof(T2) == CC::STAGE_BYTES, "row tiles and column tiles share the stage");
+        static_assert(CC::OBOX_ROWS == CC::BOX_ROWS, "loads and stores of column tiles use one tensor map");
     };
 
     // kargs: in / out = the images (p[0], os[1] = image stride in elements; rows back to back),
@@ -197,6 +200,8 @@ namespace b200fft
             const bool     is_rows = off < (unsigned)F::TR;
             const bool     landed  = ptx::mbar_wait(full, phase);
             phase ^= 1u;
+            if(tid == 0)
+                ptx::bulk_wait_read<0>(); // tensor stores of an earlier column tile have read the exchange buffer
             C2 r[32];
             if(landed)
             {
@@ -236,6 +241,7 @@ namespace b200fft
                     if(err)
                         atomicExch(err, 1);
                     ptx::mbar_wait(full, phase ^ 1u);
+                    ptx::bulk_wait_all(); // our own stores
                 }
                 __syncthreads();
                 return;
@@ -286,7 +292,12 @@ namespace b200fft
                         orow[N + lane + 32 * j] = make_float2(r[j].x.v.y, r[j].y.v.y);
                     }
                     else
-                        orow[lane + 32 * j] = make_double2(r[j].x, r[j].y);
+                    {
+                        T2 o;
+                        o.x                 = r[j].x;
+                        o.y                 = r[j].y;
+                        orow[lane + 32 * j] = o;
+                    }
                 }
                 // publish: every thread's stores before the counter moves
                 __threadfence();
@@ -297,12 +308,16 @@ namespace b200fft
             else
             {
                 // ---- column tile of image k-1: as in the column kernel ----
-                const unsigned  img  = k - 1, tile = off - F::TR;
-                const int       u = tid % CC::UNITS, tl = tid / CC::UNITS;
-                const long long obase = (long long)img * a.out.os[1] + (long long)tile * CC::COLS + u * CC::VEC;
-                T2*             gout  = reinterpret_cast<T2*>(a.out.p[0]) + obase;
-                b200fft_kargs const& ar = a;
-                colstream_from<CC, 0, false>(r, xs, tws, tl, u, ar, gout, obase, sx, sy);
+                // (results leave as tensor stores through the exchange buffer)
+                const unsigned img = k - 1, tile = off - F::TR;
+                const int      u = tid % CC::UNITS, tl = tid / CC::UNITS;
+                colstream_run<CC, 0>(r, xs, tws, tl, u);
+                colstream_store_staged<CC>(r, xs, tl, u, tid, sx, sy, [&](int row, const unsigned char* src) {
+                    const int c1 = pe == 0 ? row : (p1 == 0 ? (int)img : 0);
+                    const int c2 = pe == 1 ? row : (p1 == 1 ? (int)img : 0);
+                    const int c3 = pe == 2 ? row : (p1 == 2 ? (int)img : 0);
+                    ptx::tma_store_4d(&map, (int)(tile * (unsigned)CC::COLS * (unsigned)(sizeof(T2) / 8)), c1, c2, c3, src);
+                });
             }
             if(s_deferred)
             {
@@ -316,6 +331,8 @@ namespace b200fft
             }
             cur = nxt;
         }
+        if(tid == 0)
+            ptx::bulk_wait_all(); // nothing of ours may be in flight when the CTA retires
     }
 
     template <class C, int UN>
@@ -364,7 +381,7 @@ namespace b200fft
             return cudaErrorInvalidValue;
         const cuuint64_t dims[4]    = {(cuuint64_t)C::N * ce, (cuuint64_t)C::N, (cuuint64_t)nimages, 1};
         const cuuint64_t strides[3] = {row, istr, istr * nimages};
-        const cuuint32_t box[4]     = {(cuuint32_t)(CC::UNITS * 2), (cuuint32_t)CC::BOX_ROWS, 1, 1};
+        const cuuint32_t box[4]     = {(cuuint32_t)(CC::ROW_BYTES / 8), (cuuint32_t)CC::BOX_ROWS, 1, 1};
         const cuuint32_t estr[4]    = {1, 1, 1, 1};
         alignas(64) CUtensorMap map;
         if(enc(&map,

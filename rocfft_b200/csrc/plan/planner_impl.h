@@ -501,9 +501,9 @@ namespace b200fft
                 fill_outer(o, a, st.loops);
                 // Column tiles with 128-byte-wide rows.  Two designs exist:
                 //  * the persistent TMA-fed kernel (stockham_colstream.cuh): tensor-copy loads of the next
-                //    tile in flight while the current one is transformed, packed fp32 arithmetic on two
-                //    columns per thread; default for 1024 points in both precisions
-                //    (ROCFFT_B200_COLTMA=1 extends it to every length it exists for,
+                //    tile in flight while the current one is transformed, results out through tensor
+                //    stores; default for every length it exists for (256, 512, 1024; both precisions)
+                //    once the stage has a few tiles per SM (ROCFFT_B200_COLTMA=1: always,
                 //    ROCFFT_B200_NO_COLTMA forbids it);
                 //  * cluster-of-two kernels over distributed shared memory (ROCFFT_B200_COLCLUSTER forces
                 //    them, ROCFFT_B200_NO_COLCLUSTER forbids them).  Measured (fp32): the push-exchange
@@ -517,8 +517,10 @@ namespace b200fft
                     = prec_ == 0 && s.n <= 1024 && (s.n >= 1024 || (s.n >= 512 && pitch_bytes >= (1ll << 20)));
                 // (stores into peer GPUs' buffers keep the cluster kernel: measured on two GPUs, 1024^3, passes A / B
                 // 3.04 ms with it against 3.20 ms with the TMA-fed kernel)
+                // (the TMA-fed kernel is persistent: below a few tiles per SM the tile kernels' many small CTAs win)
+                const unsigned long long tma_tiles = (unsigned long long)(a.on[0] / 8) * a.on[1] * a.on[2];
                 const bool prefer_tma = !getenv("ROCFFT_B200_NO_COLTMA") && !getenv("ROCFFT_B200_COLCLUSTER")
-                                        && ((s.n == 1024 && !s.out_blk_ptrs) || getenv("ROCFFT_B200_COLTMA"));
+                                        && ((!s.out_blk_ptrs && (s.n == 1024 || tma_tiles >= 1024)) || getenv("ROCFFT_B200_COLTMA"));
                 if((kern->variant == B200FFT_COL_STR || kern->variant == B200FFT_COL_BLK)
                    && (prefer_tma || getenv("ROCFFT_B200_COLCLUSTER")
                        || ((s.out_blk_ptrs || prefer_cluster) && !getenv("ROCFFT_B200_NO_COLCLUSTER"))))
