@@ -4,7 +4,7 @@
 // Role in the reference: the 2D plans RTRT / RC (library/src/tree_node_2D.cpp:31-211,
 // row FFTs, transposes or a fused row/column pair, column FFTs) make two to four trips
 // through device memory per image.  B200's L2 (126 MB) holds several 1024 x 1024 images,
-// so here the row pass of image k and the column pass of image k-1 are interleaved in one
+// so here the row pass of image k and the column pass of image k-D (D = 1 to 3) are interleaved in one
 // launch: the rows of an image are read from HBM, transformed and written back (the lines
 // stay dirty in L2), and a short while later the column tiles of the same image are read
 // back — from L2 — transformed and written for good.  Per image the device memory sees one
@@ -12,8 +12,9 @@
 // planes and makes one more pass for Z.
 //
 // Work list.  Item i belongs to block k = i / (TR + TC): the first TR items of a block are
-// the row tiles of image k, the remaining TC items the column tiles of image k-1 (block 0
-// has no column part, the last block no row part).  CTA c takes items c, c + G, c + 2G, ...
+// the row tiles of image k, the remaining TC items the column tiles of image k-D (the first D
+// blocks have no column part, the last D no row part; D is chosen by the launcher: 1 in double
+// precision, 3 in single, from measurements).  CTA c takes items c, c + G, c + 2G, ...
 // in order.  A column tile may only be loaded once all TR row tiles of its image are
 // stored: every CTA that finishes a row tile makes its stores visible (fence) and adds one
 // to the image's counter; the thread that issues a column tile's loads first waits — with a
@@ -112,7 +113,9 @@ namespace b200fft
         int*    done = reinterpret_cast<int*>(const_cast<void*>(a.aux[1]));
         const unsigned nimg = a.on[1];
         constexpr unsigned B = F::TR + F::TC;
-        const unsigned long long nitems = (unsigned long long)(nimg + 1) * B;
+        // column tiles run D images behind the row tiles
+        const unsigned D = (unsigned)a.iaux[2];
+        const unsigned long long nitems = (unsigned long long)(nimg + D) * B;
         const int pe = (int)(a.iaux[3] & 3), p1 = (int)((a.iaux[3] >> 2) & 3);
 
         // twiddles of the second pass in shared memory (both tile kinds use the same 32 x 32 table)
@@ -131,7 +134,7 @@ namespace b200fft
             for(; i < nitems; i += gridDim.x)
             {
                 const unsigned k = (unsigned)(i / B), off = (unsigned)(i % B);
-                if(off < (unsigned)F::TR ? k < nimg : k >= 1)
+                if(off < (unsigned)F::TR ? k < nimg : k >= D)
                     return i;
             }
             return nitems;
@@ -151,7 +154,7 @@ namespace b200fft
                     ptx::bulk_load(reinterpret_cast<unsigned char*>(stage) + q * CHUNK, src + q * CHUNK, CHUNK, full);
                 return true;
             }
-            const unsigned img = k - 1, tile = off - F::TR;
+            const unsigned img = k - D, tile = off - F::TR;
             bool ready = false;
             for(unsigned p = 0; p < polls && !ready; ++p)
                 ready = ptx::ld_acquire_gpu(done + img) >= F::TR;
@@ -307,9 +310,9 @@ namespace b200fft
             }
             else
             {
-                // ---- column tile of image k-1: as in the column kernel ----
+                // ---- column tile of image k-D: as in the column kernel ----
                 // (results leave as tensor stores through the exchange buffer)
-                const unsigned img = k - 1, tile = off - F::TR;
+                const unsigned img = k - D, tile = off - F::TR;
                 const int      u = tid % CC::UNITS, tl = tid / CC::UNITS;
                 colstream_run<CC, 0>(r, xs, tws, tl, u);
                 colstream_store_staged<CC>(r, xs, tl, u, tid, sx, sy, [&](int row, const unsigned char* src) {
@@ -407,7 +410,16 @@ namespace b200fft
         if(e != cudaSuccess)
             return e;
         unsigned long long grid  = (unsigned long long)blocks_per_sm[dev] * sm_count[dev];
-        const unsigned long long items = (nimages + 1) * (unsigned long long)(F::TR + F::TC);
+        // distance (in images) between the row tiles and the column tiles handed out together; every image in
+        // flight lives in L2 meanwhile.  Measured on 1024 x 1024 images: double precision (16 MB per image) is
+        // fastest at 1 (0.668 ms per 64 images; 0.675 / 0.716 / 0.741 at 2 / 3 / 4), single precision at 3
+        // (1.376 ms per 256 images; 1.486 / 1.424 / 1.403 at 1 / 2 / 4).  B200FFT_2D_L2_DEPTH overrides.
+        static const char* depth_env = getenv("B200FFT_2D_L2_DEPTH");
+        unsigned long long depth     = sizeof(T2) == 8 ? 3 : 1;
+        if(depth_env && atoi(depth_env) >= 1 && atoi(depth_env) <= 16)
+            depth = (unsigned long long)atoi(depth_env);
+        ka.iaux[2] = (long long)depth;
+        const unsigned long long items = (nimages + depth) * (unsigned long long)(F::TR + F::TC);
         if(grid > items)
             grid = items;
         // CTAs wait for one another's row tiles: all of them must be resident, hence a cooperative launch
