@@ -136,11 +136,19 @@ def test_planner_choices_for_benchmark_configs(L, monkeypatch):
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 64)
     text = describe(L, p)
     assert "steps: 1" in text and "fft2d_l2_dp_1024x1024" in text and p.work_bytes == 0
-    # config 5: three in-place passes (rows, then the TMA-fed column kernel twice), no transposes, no work buffer;
-    # in single precision the fused kernel is opt-in (measured: no gain)
+    # config 5: three passes (rows in place, then the TMA-fed column kernel twice), no transposes; the slowest
+    # dimension (rows 8 MB apart) goes out of the caller's array into one volume of work space and the middle
+    # dimension comes back from there; in single precision the fused kernel is opt-in (measured: no gain)
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
+    text = describe(L, p)
+    assert "steps: 3" in text and text.count("col_tma") == 2 and p.work_bytes == 8 * 1024 ** 3
+    assert "in+0 -> temp+0" in text and "temp+0 -> in+0" in text
+    # with the work-array plan switched off: three in-place passes, no work buffer
+    monkeypatch.setenv("ROCFFT_B200_NO_LONG_PITCH_PLAN", "1")
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
     text = describe(L, p)
     assert "steps: 3" in text and text.count("col_tma") == 2 and p.work_bytes == 0
+    monkeypatch.delenv("ROCFFT_B200_NO_LONG_PITCH_PLAN")
     monkeypatch.setenv("ROCFFT_B200_2D_L2", "1")
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
     text = describe(L, p)
@@ -152,7 +160,7 @@ def test_planner_choices_for_benchmark_configs(L, monkeypatch):
     text = describe(L, p)
     assert "steps: 2" in text and "col" in text and p.work_bytes == 0
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
-    assert "steps: 3" in describe(L, p) and p.work_bytes == 0
+    assert "steps: 3" in describe(L, p) and p.work_bytes == 8 * 1024 ** 3
     monkeypatch.delenv("ROCFFT_B200_NO_2D_L2")
     # a single image is not worth the interleaved schedule
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 1)

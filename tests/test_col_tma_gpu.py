@@ -72,3 +72,26 @@ def test_device_error_flag_stays_clear(gpu):
     ref = np.fft.fft(x.astype(np.complex128), axis=0)
     assert np.linalg.norm(d.cpu().numpy() - ref) / np.linalg.norm(ref) < 5e-6
     p.destroy()
+
+
+# Volumes whose slowest dimension has a row pitch of 4 MB or more take the work-array plan: rows in the
+# caller's array, the slowest dimension out of it into a work array, the middle dimension back.
+CASES_LONG_PITCH = [
+    Case(C2C_FWD, "single", [1024, 512, 256], 1, IP),
+    Case(C2C_INV, "single", [1024, 512, 256], 1, OOP, scale=1.0 / 4096),
+    Case(C2C_FWD, "single", [2048, 256, 256], 2, IP),
+    Case(C2C_FWD, "double", [512, 512, 256], 1, OOP),
+    Case(C2C_INV, "double", [1024, 256, 256], 1, IP),
+]
+
+
+@pytest.mark.parametrize("case", CASES_LONG_PITCH, ids=lambda c: c.ident())
+def test_long_pitch_volumes_use_a_work_array(gpu, case, monkeypatch):
+    text = _plan_text(case)
+    assert text.count("col_tma") == 2 and "work" in text.lower(), text
+    ok, msg = run_case(case)
+    assert ok, f"{case.ident()}: {msg}"
+    # the plain three in-place passes give the same answer
+    monkeypatch.setenv("ROCFFT_B200_NO_LONG_PITCH_PLAN", "1")
+    ok, msg = run_case(case)
+    assert ok, f"{case.ident()} (plain plan): {msg}"
