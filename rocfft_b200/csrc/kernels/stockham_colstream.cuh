@@ -688,8 +688,9 @@ namespace b200fft
         if(!colstream_tile_map(&map, &perm, a.in, a, (unsigned)C::N, sizeof(T2), (unsigned)CC::BOX_ROWS))
             return cudaErrorInvalidValue;
         bool ts = false;
+        // (bit 32 of iaux[3], set by the planner: the output is another GPU's memory, keep to plain stores)
         if constexpr(CAN_TS)
-            ts = !reg_stores && (reinterpret_cast<size_t>(a.out.p[0]) % 16 == 0)
+            ts = !reg_stores && !(a.iaux[3] & (1ll << 32)) && (reinterpret_cast<size_t>(a.out.p[0]) % 16 == 0)
                  && colstream_tile_map(&omap, &operm, a.out, a, (unsigned)C::N, sizeof(T2), (unsigned)CC::OBOX_ROWS);
         if(!ts)
             omap = map;

@@ -500,6 +500,7 @@ namespace b200fft
                 s.in           = Rb;
                 s.out          = R2b;
                 s.out_blk_ptrs = sp->tab_b;
+                s.peer_out     = P > 1;
                 s.inverse      = inverse;
                 p.emit_c2c_1d(s);
                 sp->passB.push_back(std::move(core));
@@ -567,6 +568,7 @@ namespace b200fft
                     s.out            = Rb;
                     s.out.byte_off[0]
                         = reinterpret_cast<size_t>(sp->peer_r[q]) + (size_t)sp->rank * lz * ny * lx * sp->csize;
+                    s.peer_out = q != sp->rank;
                     s.inverse = inverse;
                     p.emit_c2c_1d(s);
                 }
@@ -618,6 +620,7 @@ namespace b200fft
                 s.out.byte_off[0] = sp->off_s + c * (sp->slab_bytes / kA);
                 if(sp->p2p)
                     s.out_blk_ptrs = sp->tab_a;
+                s.peer_out = sp->p2p && P > 1;
                 s.inverse        = inverse;
                 p.emit_c2c_1d(s);
                 sp->passA.push_back(std::move(core));
@@ -641,6 +644,7 @@ namespace b200fft
                 s.out.byte_off[0] = sp->off_s + c * chunk_bytes;
                 if(sp->p2p)
                     s.out_blk_ptrs = sp->tab_b + (size_t)c * P;
+                s.peer_out = sp->p2p && P > 1;
                 s.inverse         = inverse;
                 p.emit_c2c_1d(s);
                 sp->passB.push_back(std::move(core));

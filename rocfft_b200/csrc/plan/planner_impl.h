@@ -34,6 +34,8 @@ namespace b200fft
             size_t       out_blk = 0;
             ptrdiff_t    out_bs  = 0;
             void* const* out_blk_ptrs = nullptr; // device table: one base pointer per block
+            // the output lies in another GPU's memory: kernels keep to plain stores issued by their threads
+            bool peer_out = false;
             // fused kernels: a specific pool variant and its extra table
             int         force_variant = -1;
             const void* aux0          = nullptr;
@@ -640,6 +642,7 @@ namespace b200fft
                 a.aux[1]    = s.aux1;
                 a.iaux[0]   = s.iaux0;
                 a.iaux[1]   = s.max_ctas;
+                a.iaux[3]   = s.peer_out ? (1ll << 32) : 0; // column kernels: no tensor stores
                 a.aux[2]    = s.lt_tab;
                 a.iaux[2]   = s.lt_steps;
                 st.ntiles   = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];
