@@ -82,6 +82,12 @@ CASES_LONG_PITCH = [
     Case(C2C_FWD, "single", [2048, 256, 256], 2, IP),
     Case(C2C_FWD, "double", [512, 512, 256], 1, OOP),
     Case(C2C_INV, "double", [1024, 256, 256], 1, IP),
+    # padded rows and planes on both sides (in place), different layouts in and out (out of place), no caller work buffer
+    Case(C2C_FWD, "single", [1024, 512, 256], 1, IP, in_strides=[1, 1040, 1040 * 514], out_strides=[1, 1040, 1040 * 514],
+         in_dist=1040 * 514 * 256, out_dist=1040 * 514 * 256),
+    Case(C2C_FWD, "single", [1024, 512, 256], 1, OOP, in_strides=[1, 1026, 1026 * 512], in_dist=1026 * 512 * 256,
+         out_strides=[1, 1024, 1024 * 520], out_dist=1024 * 520 * 256),
+    Case(C2C_FWD, "single", [1024, 512, 256], 1, IP, user_work_buffer=False),
 ]
 
 
