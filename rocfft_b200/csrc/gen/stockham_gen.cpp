@@ -507,6 +507,24 @@ int main(int argc, char** argv)
         }
     }
 
+    // ---- Bluestein with one warp per 1024-point row of the padded length (bluestein_rc.cuh) ----
+    // single precision, M = 20 x 1024: the length the single-kernel form reaches in 227 KB of shared memory
+    if(!g_small)
+    {
+        Kernel k;
+        k.n       = 20480;
+        k.prec    = 0;
+        k.variant = 27;
+        k.tpt     = 640;
+        k.tpb     = 1;
+        k.minb    = 1;
+        k.f       = {32, 32}; // the 1024-point rows: the stacked twiddle table the planner builds
+        k.smem    = (size_t)20480 * 8 + 31 * 32 * 8;
+        k.name    = "fft_sp_len20480_row_blue_rc";
+        k.cfg     = "KCfg<float,20480,640,1,false,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE,1,FactorList<32,32>>";
+        kernels.push_back(k);
+    }
+
     // ---- small 2D transforms in one kernel (stockham_2d.cuh) ----
     // Both dimensions come from one family with a common number of points per thread, so that
     // the row phase and the column phase use the same threads: powers of two with 8 points per
@@ -624,7 +642,7 @@ int main(int argc, char** argv)
     {
         files[i].open(outdir + "/gen_kernels_" + std::to_string(i) + ".cu");
         files[i] << "// GENERATED by stockham_gen — do not edit.\n"
-                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_colstream.cuh\"\n#include \"stockham_fused2d.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
+                    "#include \"gen_butterflies.cuh\"\n#include \"stockham_rows_tma.cuh\"\n#include \"stockham_colpair.cuh\"\n#include \"stockham_colcluster.cuh\"\n#include \"stockham_colpush.cuh\"\n#include \"stockham_colstream.cuh\"\n#include \"stockham_fused2d.cuh\"\n#include \"bluestein_rc.cuh\"\n#include \"stockham_2d.cuh\"\nusing namespace b200fft;\n\n";
     }
     for(size_t oi = 0; oi < order.size(); ++oi)
     {
@@ -635,6 +653,8 @@ int main(int argc, char** argv)
           << "    return ";
         if(k.variant == 9)
             o << "launch_bluestein_kernel<" << k.cfg << ">";
+        else if(k.variant == 27)
+            o << "launch_bluestein_rc_kernel<" << k.cfg << ", " << k.n / 1024 << ">";
         else if(k.variant >= 10 && k.variant <= 12)
             o << "launch_rows_tma_kernel<" << k.cfg << ", " << (k.variant - 10) << ", " << kTmaStages << ">";
         else if(k.variant >= 23 && k.variant <= 25)

@@ -58,6 +58,9 @@ typedef enum b200fft_variant
     B200FFT_ROW_TMA_PK     = 23,
     B200FFT_ROW_R2C_TMA_PK = 24,
     B200FFT_ROW_C2R_TMA_PK = 25,
+    // whole Bluestein transform in one kernel, padded length = rows x 1024, one warp per row (bluestein_rc.cuh);
+    // `length` is the padded length
+    B200FFT_ROW_BLUE_RC = 27,
 } b200fft_variant;
 
 typedef cudaError_t (*b200fft_tile_launcher)(const b200fft_kargs*, unsigned long long ntiles, cudaStream_t);

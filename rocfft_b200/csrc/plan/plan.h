@@ -181,4 +181,6 @@ namespace b200fft
     void host_large_twiddles(size_t n, int precision, int* steps, std::vector<char>& out); // base-256 stepped table
     void host_chirp(size_t n, int precision, std::vector<char>& out); // exp(-i pi p^2/n), p < n
     void host_bluestein_filter(size_t n, size_t m, int precision, std::vector<char>& out); // FFT_m(wrapped conj chirp)/m
+    // the same filter in [k2][k1] order and W_m^(n1 k2) in [k2][n1] order for m = rows x cols (bluestein_rc.cuh)
+    void host_bluestein_rc_tables(size_t n, size_t rows, size_t cols, int precision, std::vector<char>& filt, std::vector<char>& twm);
 }

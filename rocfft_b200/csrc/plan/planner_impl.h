@@ -40,6 +40,7 @@ namespace b200fft
             int         force_variant = -1;
             const void* aux0          = nullptr;
             const void* aux1          = nullptr;
+            const void* aux2          = nullptr; // third table of a fused kernel (kernel argument aux[2], unless lt_tab uses it)
             long long   iaux0         = 0;
             size_t      kernel_length = 0; // pool length when it differs from n (Bluestein: padded length)
             // second kernel of a long 1D transform: multiply the input by W^(k1 * e), k1 = index of outer[0]
@@ -643,7 +644,7 @@ namespace b200fft
                 a.iaux[0]   = s.iaux0;
                 a.iaux[1]   = s.max_ctas;
                 a.iaux[3]   = s.peer_out ? (1ll << 32) : 0; // column kernels: no tensor stores
-                a.aux[2]    = s.lt_tab;
+                a.aux[2]    = s.lt_tab ? s.lt_tab : s.aux2;
                 a.iaux[2]   = s.lt_steps;
                 st.ntiles   = (unsigned long long)a.ntile0 * a.on[1] * a.on[2];
                 st.in_elem_bytes  = elem_bytes(s.in);
@@ -778,6 +779,21 @@ namespace b200fft
                     std::vector<char> h;
                     host_chirp(s.n, prec_, h);
                     const void* chirp = upload(h);
+                    // padded lengths that are a whole number of 1024-point rows: one warp per row (bluestein_rc.cuh)
+                    if(mf % 1024 == 0 && pool_find(mf, prec_, B200FFT_ROW_BLUE_RC) && !getenv("ROCFFT_B200_NO_BLUE_RC"))
+                    {
+                        std::vector<char> hf, ht;
+                        host_bluestein_rc_tables(s.n, mf / 1024, 1024, prec_, hf, ht);
+                        Stage f         = s;
+                        f.force_variant = B200FFT_ROW_BLUE_RC;
+                        f.kernel_length = mf;
+                        f.aux0          = chirp;
+                        f.aux1          = upload(hf);
+                        f.aux2          = upload(ht);
+                        f.iaux0         = (long long)s.n;
+                        emit_tile(f);
+                        return;
+                    }
                     host_bluestein_filter(s.n, mf, prec_, h);
                     Stage f         = s;
                     f.force_variant = B200FFT_ROW_BLUE;

@@ -186,4 +186,32 @@ namespace b200fft
         for(size_t k = 0; k < m; ++k)
             push(out, precision, b[k] / (ld)m);
     }
+
+    // Tables of the row-per-warp Bluestein kernel (bluestein_rc.cuh) for the padded length m = rows x cols:
+    // the filter of host_bluestein_filter in [k2][k1] order (entry k2 * cols + k1 = filter[rows * k1 + k2]) and
+    // the twiddles between its two levels, W_m^(n1 k2) at k2 * cols + n1.
+    void host_bluestein_rc_tables(size_t n, size_t rows, size_t cols, int precision, std::vector<char>& filt, std::vector<char>& twm)
+    {
+        const size_t       m = rows * cols;
+        std::vector<cld>   b(m, cld(0, 0));
+        unsigned long long sq = 0;
+        const unsigned long long m2 = 2ull * n;
+        for(size_t p = 0; p < n; ++p)
+        {
+            cld c = std::conj(unit_root(sq, m2)); // exp(+i pi p^2 / n)
+            b[p]  = c;
+            if(p)
+                b[m - p] = c;
+            sq = (sq + 2ull * p + 1) % m2;
+        }
+        host_fft(b);
+        filt.clear();
+        twm.clear();
+        for(size_t k2 = 0; k2 < rows; ++k2)
+            for(size_t k1 = 0; k1 < cols; ++k1)
+            {
+                push(filt, precision, b[rows * k1 + k2] / (ld)m);
+                push(twm, precision, unit_root((unsigned long long)k1 * k2, m));
+            }
+    }
 }
