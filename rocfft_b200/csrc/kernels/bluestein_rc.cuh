@@ -15,8 +15,8 @@
 //             inputs, odd k2 from the inputs times W_R^n2); times W_M^(n1 k2); into the shared tile [k2][n1];
 //   rows      warp k2: the 1024-point transform over n1 as 32 x 32 with one point column per lane and the
 //             exchange inside the warp (no CTA barrier), times the filter (stored [k2][k1] by the host),
-//             the inverse 1024-point transform the same way, times conj W_M^(m1 k2), back into the tile;
-//   columns   thread per m1: the inverse R-point DFT over k2, of which only the outputs m2 < R/2 are
+//             the inverse 1024-point transform the same way, back into the tile;
+//   columns   thread per m1: times conj W_M^(m1 k2), then the inverse R-point DFT over k2, of which only the outputs m2 < R/2 are
 //             wanted (again two R/2-point butterflies), times the chirp, to global memory.
 //
 // Two CTA barriers per transform instead of twelve; in the row phase, which is most of the work,
@@ -116,28 +116,79 @@ namespace b200fft
             wr[j].y = -s;
         }
 
-        // ---- columns, forward ----
-        for(int c = tid; c < CN; c += B::THREADS)
+        // ---- columns, forward (the loads of all of a thread's columns are issued before any arithmetic) ----
+        constexpr int ROUNDS = (CN + B::THREADS - 1) / B::THREADS;
         {
-            T2 v[H], w[H];
-#pragma unroll
-            for(int j = 0; j < H; ++j)
+            // Every load of the input is issued before anything depends on one: clamped indices instead of
+            // branches (points past the end are read from the last point and zeroed afterwards), the planar /
+            // interleaved decision outside the loops.  With a branch and a multiply behind each load the
+            // twenty device-memory round trips of a thread ran one after the other (measured: 19 000 of the
+            // phase's 25 000 cycles).
+            T2 v[ROUNDS][H];
+            const long long es = a.in.es;
+            if(a.in.planar)
             {
-                const int e = c + CN * j;
-                v[j].x = v[j].y = 0.0f;
-                if(e < n)
-                    v[j] = cmul(gload<C>(a.in, ibase, e, inverse), chirp[e]);
+                const float* __restrict__ p0 = reinterpret_cast<const float*>(a.in.p[0]);
+                const float* __restrict__ p1 = reinterpret_cast<const float*>(a.in.p[1]);
+#pragma unroll
+                for(int q = 0; q < ROUNDS; ++q)
+#pragma unroll
+                    for(int j = 0; j < H; ++j)
+                    {
+                        const int       e   = min(min(tid + q * B::THREADS, CN - 1) + CN * j, n - 1);
+                        const long long off = ibase + (long long)e * es;
+                        v[q][j].x           = p0[off];
+                        v[q][j].y           = p1[off];
+                    }
+            }
+            else
+            {
+                const T2* __restrict__ p0 = reinterpret_cast<const T2*>(a.in.p[0]);
+#pragma unroll
+                for(int q = 0; q < ROUNDS; ++q)
+#pragma unroll
+                    for(int j = 0; j < H; ++j)
+                    {
+                        const int e = min(min(tid + q * B::THREADS, CN - 1) + CN * j, n - 1);
+                        v[q][j]     = p0[ibase + (long long)e * es];
+                    }
             }
 #pragma unroll
-            for(int j = 0; j < H; ++j)
-                w[j] = cmul(v[j], wr[j]);
-            Butterfly<H, T2>::run(v);
-            Butterfly<H, T2>::run(w);
-#pragma unroll
-            for(int m = 0; m < H; ++m)
+            for(int q = 0; q < ROUNDS; ++q)
             {
-                tile[(2 * m) * CN + c]     = cmul(v[m], twm[(2 * m) * CN + c]);
-                tile[(2 * m + 1) * CN + c] = cmul(w[m], twm[(2 * m + 1) * CN + c]);
+                T2 ch[H];
+#pragma unroll
+                for(int j = 0; j < H; ++j)
+                    ch[j] = chirp[min(min(tid + q * B::THREADS, CN - 1) + CN * j, n - 1)];
+#pragma unroll
+                for(int j = 0; j < H; ++j)
+                {
+                    const bool live = tid + q * B::THREADS + CN * j < n;
+                    const T2   x    = inverse ? cswap(v[q][j]) : v[q][j];
+                    const T2   y    = cmul(x, ch[j]);
+                    v[q][j].x       = live ? y.x : 0.0f;
+                    v[q][j].y       = live ? y.y : 0.0f;
+                }
+            }
+#pragma unroll
+            for(int q = 0; q < ROUNDS; ++q)
+            {
+                const int c = tid + q * B::THREADS;
+                if(c < CN)
+                {
+                    T2 w[H];
+#pragma unroll
+                    for(int j = 0; j < H; ++j)
+                        w[j] = cmul(v[q][j], wr[j]);
+                    Butterfly<H, T2>::run(v[q]);
+                    Butterfly<H, T2>::run(w);
+#pragma unroll
+                    for(int m = 0; m < H; ++m)
+                    {
+                        tile[(2 * m) * CN + c]     = cmul(v[q][m], twm[(2 * m) * CN + c]);
+                        tile[(2 * m + 1) * CN + c] = cmul(w[m], twm[(2 * m + 1) * CN + c]);
+                    }
+                }
             }
         }
         __syncthreads();
@@ -156,40 +207,59 @@ namespace b200fft
             for(int j = 0; j < 32; ++j)
                 r[j] = cswap(cmul(r[j], f[lane + 32 * j]));
             warp_fft1024(r, xw, tws, lane);
-            const T2* __restrict__ t = twm + warp * CN;
-#pragma unroll
-            for(int j = 0; j < 32; ++j)
-                r[j] = cmulc(cswap(r[j]), t[lane + 32 * j]);
             __syncwarp();
 #pragma unroll
             for(int j = 0; j < 32; ++j)
-                row[lane + 32 * j] = r[j];
+                row[lane + 32 * j] = r[j]; // parts still exchanged and the twiddle still owed: the column phase does both
         }
+        // the twiddles and chirp values of this thread's first column travel while the barrier is waited for
+        T2 tv[R], cv[H];
+#pragma unroll
+        for(int k = 0; k < R; ++k)
+            tv[k] = twm[k * CN + tid];
+#pragma unroll
+        for(int m2 = 0; m2 < H; ++m2)
+            cv[m2] = (tid + CN * m2 < n) ? chirp[tid + CN * m2] : make_float2(0.0f, 0.0f);
         __syncthreads();
 
         // ---- columns, inverse; outputs m2 < R/2 only ----
-        for(int c = tid; c < CN; c += B::THREADS)
+#pragma unroll
+        for(int q = 0; q < ROUNDS; ++q)
         {
-            T2 ev[H], od[H];
-#pragma unroll
-            for(int m = 0; m < H; ++m)
+            const int c = tid + q * B::THREADS;
+            if(c < CN)
             {
-                ev[m] = cswap(tile[(2 * m) * CN + c]);
-                od[m] = cswap(tile[(2 * m + 1) * CN + c]);
-            }
-            Butterfly<H, T2>::run(ev);
-            Butterfly<H, T2>::run(od);
-#pragma unroll
-            for(int m2 = 0; m2 < H; ++m2)
-            {
-                const int e = c + CN * m2;
-                if(e < n)
+                if(q > 0)
                 {
-                    const T2 o = cmulc(cswap(od[m2]), wr[m2]);
-                    T2       y = cswap(ev[m2]);
-                    y.x += o.x;
-                    y.y += o.y;
-                    gstore<C>(a.out, obase, e, cmul(y, chirp[e]), inverse, use_sc, scale);
+#pragma unroll
+                    for(int k = 0; k < R; ++k)
+                        tv[k] = twm[k * CN + c];
+#pragma unroll
+                    for(int m2 = 0; m2 < H; ++m2)
+                        cv[m2] = (c + CN * m2 < n) ? chirp[c + CN * m2] : make_float2(0.0f, 0.0f);
+                }
+                T2 ev[H], od[H];
+#pragma unroll
+                for(int m = 0; m < H; ++m)
+                {
+                    // tile holds swap(U); V = U conj(W_M^(m1 k2)); the R/2-point inverse DFTs run on swap(V)
+                    ev[m] = cswap(cmulc(cswap(tile[(2 * m) * CN + c]), tv[2 * m]));
+                    od[m] = cswap(cmulc(cswap(tile[(2 * m + 1) * CN + c]), tv[2 * m + 1]));
+                }
+                Butterfly<H, T2>::run(ev);
+                Butterfly<H, T2>::run(od);
+#pragma unroll
+                for(int m2 = 0; m2 < H; ++m2)
+                {
+                    const int e = c + CN * m2;
+                    if(e < n)
+                    {
+                        const T2 o = cmulc(cswap(od[m2]), wr[m2]);
+                        T2       y = cswap(ev[m2]);
+                        y.x += o.x;
+                        y.y += o.y;
+                        gstore<C>(a.out, obase, e, cmul(y, cv[m2]), inverse, use_sc, scale);
+                    }
                 }
             }
         }
