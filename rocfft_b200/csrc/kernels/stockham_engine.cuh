@@ -765,15 +765,20 @@ namespace b200fft
 
         const unsigned  nvalid = min((unsigned)C::TPB, a.on[0] - tp.i0_first);
         const bool      valid  = (unsigned)c < nvalid;
-        const long long ibase  = view_base(a.in, tp.i0_first + c, tp.i1, tp.i2);
+        // (slots past the last transform read the tile's first transform and discard it)
+        const long long ibase  = view_base(a.in, tp.i0_first + (valid ? c : 0), tp.i1, tp.i2);
         const long long obase  = view_base(a.out, tp.i0_first + c, tp.i1, tp.i2);
 
+        // branch-free (clamped index, result zeroed afterwards): with a branch around the load and the
+        // multiply behind it the loads of a pass ran one after the other instead of back to back
         auto src1 = [&](int e) -> T2 {
-            T2 v;
-            v.x = 0;
-            v.y = 0;
-            if(valid && e < n)
-                v = cmul(gload<C>(a.in, ibase, e, inverse), chirp[e]);
+            const int  ec   = min(e, n - 1);
+            const T2   x    = gload<C>(a.in, ibase, ec, inverse);
+            const T2   w    = chirp[ec];
+            const bool live = valid && e < n;
+            T2         v    = cmul(x, w);
+            v.x             = live ? v.x : (T)0;
+            v.y             = live ? v.y : (T)0;
             return v;
         };
         auto s_dst = [=](int e, T2 v) { sm[C::sidx(c, e)] = v; };
