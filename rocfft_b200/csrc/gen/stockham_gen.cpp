@@ -508,22 +508,24 @@ int main(int argc, char** argv)
     }
 
     // ---- Bluestein with one warp per 1024-point row of the padded length (bluestein_rc.cuh) ----
-    // single precision, M = 20 x 1024: the length the single-kernel form reaches in 227 KB of shared memory
+    // single precision, M = R x 1024 with an even R: 6144 ... 20480 (the longest that fits 227 KB of shared memory)
     if(!g_small)
-    {
-        Kernel k;
-        k.n       = 20480;
-        k.prec    = 0;
-        k.variant = 27;
-        k.tpt     = 640;
-        k.tpb     = 1;
-        k.minb    = 1;
-        k.f       = {32, 32}; // the 1024-point rows: the stacked twiddle table the planner builds
-        k.smem    = (size_t)20480 * 8 + 31 * 32 * 8;
-        k.name    = "fft_sp_len20480_row_blue_rc";
-        k.cfg     = "KCfg<float,20480,640,1,false,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE,1,FactorList<32,32>>";
-        kernels.push_back(k);
-    }
+        for(int rows : {6, 8, 10, 12, 16, 20})
+        {
+            Kernel k;
+            k.n       = rows * 1024;
+            k.prec    = 0;
+            k.variant = 27;
+            k.tpt     = 32 * rows;
+            k.tpb     = 1;
+            k.minb    = rows <= 6 ? 3 : (rows <= 12 ? 2 : 1);
+            k.f       = {32, 32}; // the 1024-point rows: the stacked twiddle table the planner builds
+            k.smem    = (size_t)k.n * 8 + 31 * 32 * 8;
+            k.name    = "fft_sp_len" + std::to_string(k.n) + "_row_blue_rc";
+            k.cfg     = "KCfg<float," + std::to_string(k.n) + "," + std::to_string(k.tpt)
+                    + ",1,false,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE," + std::to_string(k.minb) + ",FactorList<32,32>>";
+            kernels.push_back(k);
+        }
 
     // ---- small 2D transforms in one kernel (stockham_2d.cuh) ----
     // Both dimensions come from one family with a common number of points per thread, so that

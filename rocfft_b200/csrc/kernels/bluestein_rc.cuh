@@ -41,6 +41,8 @@ namespace b200fft
         static constexpr size_t TILE_BYTES = (size_t)M * 8;
         static constexpr int    TW_ENTRIES = 31 * 32;
         static constexpr size_t SMEM_BYTES = TILE_BYTES + (size_t)TW_ENTRIES * 8;
+        // resident CTAs per SM the launch bounds ask for: what shared memory allows, as long as ~85 registers remain
+        static constexpr int MINB = R <= 6 ? 3 : (R <= 12 ? 2 : 1);
         static_assert(R % 2 == 0 && R >= 4 && R <= 32, "even row counts up to 32");
     };
 
@@ -78,7 +80,7 @@ namespace b200fft
     }
 
     template <class C, int R>
-    __global__ void __launch_bounds__(32 * R, 1) bluestein_rc_kernel(const __grid_constant__ b200fft_kargs a)
+    __global__ void __launch_bounds__(32 * R, BlueRC<R>::MINB) bluestein_rc_kernel(const __grid_constant__ b200fft_kargs a)
     {
         using B  = BlueRC<R>;
         using T2 = float2;

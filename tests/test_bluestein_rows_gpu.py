@@ -1,5 +1,6 @@
-"""The row-per-warp Bluestein kernel (bluestein_rc.cuh; padded length 20 x 1024) against the CPU oracle:
-lengths across its range 8193 ... 10240 (primes, a composite outside the pool, the largest length it takes),
+"""The row-per-warp Bluestein kernel (bluestein_rc.cuh; padded lengths R x 1024, R = 6 ... 20) against the CPU oracle:
+lengths across the range of the largest padded length, 8193 ... 10240 (primes, a composite outside the pool, the
+largest length it takes), one or two lengths for each of the smaller padded lengths,
 forward and inverse, in place and out of place, strided and planar layouts, scale factors, several
 transforms per launch.  Bounds: rocfft-test's (shared/accuracy_test.h:1497-1498, 1609-1619)."""
 import pytest
@@ -19,6 +20,14 @@ CASES = [
     Case(C2C_INV, "single", [9973], 2, OOP, CI, CP),
     Case(C2C_FWD, "single", [10007], 4, OOP, in_strides=[3], in_dist=3 * 10007 + 5, out_strides=[2], out_dist=2 * 10007),
     Case(C2C_FWD, "single", [10007, 3], 2, OOP),                 # as the first dimension of a 2D transform
+    Case(C2C_FWD, "single", [3001], 7, OOP),                     # 6 x 1024
+    Case(C2C_INV, "single", [3067], 5, IP),
+    Case(C2C_FWD, "single", [4093], 6, IP),                      # 8 x 1024
+    Case(C2C_FWD, "single", [4099], 9, OOP),                     # 10 x 1024
+    Case(C2C_INV, "single", [5119], 4, OOP, CP, CI),
+    Case(C2C_FWD, "single", [6007], 5, OOP),                     # 12 x 1024
+    Case(C2C_FWD, "single", [8191], 3, IP),                      # 16 x 1024
+    Case(C2C_INV, "single", [7919], 4, OOP, scale=0.5),
 ]
 
 
