@@ -519,7 +519,7 @@ int main(int argc, char** argv)
             k.tpt     = 32 * rows;
             k.tpb     = 1;
             k.minb    = rows <= 6 ? 3 : (rows <= 12 ? 2 : 1);
-            k.f       = {32, 32}; // the 1024-point rows: the stacked twiddle table the planner builds
+            k.f       = {32, 32, rows}; // the stacked table's first block (992 entries) is the 32 x 32 table of the rows
             k.smem    = (size_t)k.n * 8 + 31 * 32 * 8;
             k.name    = "fft_sp_len" + std::to_string(k.n) + "_row_blue_rc";
             k.cfg     = "KCfg<float," + std::to_string(k.n) + "," + std::to_string(k.tpt)
