@@ -165,10 +165,21 @@ def test_planner_choices_for_benchmark_configs(L, monkeypatch):
     # a single image is not worth the interleaved schedule
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [1024, 1024], 1)
     assert "steps: 2" in describe(L, p)
-    # config 4: prime length goes through the single-kernel Bluestein with M = 20480
+    # config 4: prime length goes through the single-kernel Bluestein with M = 20480 = 20 x 1024, one warp per row
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)
     text = describe(L, p)
-    assert "steps: 1" in text and "len20480_row_blue" in text and p.work_bytes == 0
+    assert "steps: 1" in text and "len20480_row_blue_rc" in text and p.work_bytes == 0
+    # ... other single-precision lengths pick the smallest padded length of whole 1024-point rows the same way,
+    # double precision and switched-off plans keep the three-pass kernel
+    for n, m in ((3001, 6144), (4099, 10240), (6007, 12288), (8191, 16384)):
+        p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [n], 8)
+        assert f"len{m}_row_blue_rc" in describe(L, p), (n, describe(L, p))
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [4099], 8)
+    assert "row_blue" in describe(L, p) and "row_blue_rc" not in describe(L, p)
+    monkeypatch.setenv("ROCFFT_B200_NO_BLUE_RC", "1")
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)
+    assert "len20480_row_blue " in describe(L, p) + " " and "row_blue_rc" not in describe(L, p)
+    monkeypatch.delenv("ROCFFT_B200_NO_BLUE_RC")
     # a prime too long for one CTA's shared memory takes the multi-kernel Bluestein path
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [100003], 4)
     assert "bluestein_pad_mul" in describe(L, p) and p.work_bytes > 0
