@@ -508,24 +508,30 @@ int main(int argc, char** argv)
     }
 
     // ---- Bluestein with one warp per 1024-point row of the padded length (bluestein_rc.cuh) ----
-    // single precision, M = R x 1024 with an even R: 6144 ... 20480 (the longest that fits 227 KB of shared memory)
+    // M = R x 1024 with an even R: single precision 6144 ... 20480, double precision 6144 ... 12288 (what fits
+    // 227 KB of shared memory)
     if(!g_small)
-        for(int rows : {6, 8, 10, 12, 16, 20})
-        {
-            Kernel k;
-            k.n       = rows * 1024;
-            k.prec    = 0;
-            k.variant = 27;
-            k.tpt     = 32 * rows;
-            k.tpb     = 1;
-            k.minb    = rows <= 6 ? 3 : (rows <= 12 ? 2 : 1);
-            k.f       = {32, 32, rows}; // the stacked table's first block (992 entries) is the 32 x 32 table of the rows
-            k.smem    = (size_t)k.n * 8 + 31 * 32 * 8;
-            k.name    = "fft_sp_len" + std::to_string(k.n) + "_row_blue_rc";
-            k.cfg     = "KCfg<float," + std::to_string(k.n) + "," + std::to_string(k.tpt)
-                    + ",1,false,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE," + std::to_string(k.minb) + ",FactorList<32,32>>";
-            kernels.push_back(k);
-        }
+        for(int prec = 0; prec < 2; ++prec)
+            for(int rows : {6, 8, 10, 12, 16, 20})
+            {
+                if(prec == 1 && rows > 12)
+                    continue;
+                const int esz = prec == 0 ? 8 : 16;
+                Kernel    k;
+                k.n       = rows * 1024;
+                k.prec    = prec;
+                k.variant = 27;
+                k.tpt     = 32 * rows;
+                k.tpb     = 1;
+                k.minb    = prec == 1 ? 1 : (rows <= 6 ? 3 : (rows <= 12 ? 2 : 1));
+                k.f       = {32, 32, rows}; // the stacked table's first block (992 entries) is the 32 x 32 table of the rows
+                k.smem    = (size_t)k.n * esz + 31 * 32 * esz;
+                k.name    = std::string("fft_") + (prec == 0 ? "sp" : "dp") + "_len" + std::to_string(k.n) + "_row_blue_rc";
+                k.cfg     = std::string("KCfg<") + (prec == 0 ? "float" : "double") + "," + std::to_string(k.n) + ","
+                        + std::to_string(k.tpt) + ",1,false,IO_GENERIC,IO_GENERIC,COOP_NONE,COOP_NONE," + std::to_string(k.minb)
+                        + ",FactorList<32,32>>";
+                kernels.push_back(k);
+            }
 
     // ---- small 2D transforms in one kernel (stockham_2d.cuh) ----
     // Both dimensions come from one family with a common number of points per thread, so that

@@ -31,26 +31,27 @@
 
 namespace b200fft
 {
-    template <int R>
+    template <int R, typename T = float>
     struct BlueRC
     {
         static constexpr int    CN         = 1024; // points per row
         static constexpr int    M          = R * CN;
         static constexpr int    H          = R / 2;
         static constexpr int    THREADS    = 32 * R;
-        static constexpr size_t TILE_BYTES = (size_t)M * 8;
+        static constexpr size_t TILE_BYTES = (size_t)M * 2 * sizeof(T);
         static constexpr int    TW_ENTRIES = 31 * 32;
-        static constexpr size_t SMEM_BYTES = TILE_BYTES + (size_t)TW_ENTRIES * 8;
+        static constexpr size_t SMEM_BYTES = TILE_BYTES + (size_t)TW_ENTRIES * 2 * sizeof(T);
         // resident CTAs per SM the launch bounds ask for: what shared memory allows, as long as ~85 registers remain
-        static constexpr int MINB = R <= 6 ? 3 : (R <= 12 ? 2 : 1);
+        static constexpr int MINB = sizeof(T) == 8 ? 1 : (R <= 6 ? 3 : (R <= 12 ? 2 : 1)); // (32 double-precision points per lane: ~200 registers)
         static_assert(R % 2 == 0 && R >= 4 && R <= 32, "even row counts up to 32");
     };
 
     // forward 1024-point transform held by one warp: lane t has points t + 32 j in r[j] on entry and on exit.
-    // `xw` = 1056 floats of shared memory private to the warp; `tws` = W_1024^(j t) at [(j-1) * 32 + t].
-    __device__ __forceinline__ void warp_fft1024(float2 (&r)[32], float* xw, const float2* tws, const int lane)
+    // `xw` = 1056 components of shared memory private to the warp; `tws` = W_1024^(j t) at [(j-1) * 32 + t].
+    template <typename T, typename T2>
+    __device__ __forceinline__ void warp_fft1024(T2 (&r)[32], T* xw, const T2* tws, const int lane)
     {
-        Butterfly<32, float2>::run(r);
+        Butterfly<32, T2>::run(r);
 #pragma unroll
         for(int half = 0; half < 2; ++half)
         {
@@ -66,7 +67,7 @@ namespace b200fft
             for(int j = 0; j < 32; ++j)
             {
                 const int   e = lane + 32 * j;
-                const float v = xw[e + (e >> 5)];
+                const T     v = xw[e + (e >> 5)];
                 if(half == 0)
                     r[j].x = v;
                 else
@@ -76,15 +77,15 @@ namespace b200fft
 #pragma unroll
         for(int j = 1; j < 32; ++j)
             r[j] = cmul(r[j], tws[(j - 1) * 32 + lane]);
-        Butterfly<32, float2>::run(r);
+        Butterfly<32, T2>::run(r);
     }
 
     template <class C, int R>
-    __global__ void __launch_bounds__(32 * R, BlueRC<R>::MINB) bluestein_rc_kernel(const __grid_constant__ b200fft_kargs a)
+    __global__ void __launch_bounds__(32 * R, (BlueRC<R, typename C::T>::MINB)) bluestein_rc_kernel(const __grid_constant__ b200fft_kargs a)
     {
-        using B  = BlueRC<R>;
-        using T2 = float2;
-        static_assert(sizeof(typename C::T) == 4, "single precision");
+        using T  = typename C::T;
+        using B  = BlueRC<R, T>;
+        using T2 = typename C::T2;
         constexpr int CN = B::CN, H = B::H;
         extern __shared__ __align__(16) unsigned char smem_raw[];
         T2* tile = reinterpret_cast<T2*>(smem_raw);
@@ -96,7 +97,7 @@ namespace b200fft
         const TilePos tp      = decode_tile(a, blockIdx.x, 1);
         const bool    inverse = a.inverse != 0;
         const bool    use_sc  = a.use_scale != 0;
-        const float   scale   = (float)a.scale;
+        const T       scale   = (T)a.scale;
         const int     n       = (int)a.iaux[0];
         const T2* __restrict__ tw    = reinterpret_cast<const T2*>(a.twiddles);
         const T2* __restrict__ chirp = reinterpret_cast<const T2*>(a.aux[0]);
@@ -112,10 +113,10 @@ namespace b200fft
 #pragma unroll
         for(int j = 0; j < H; ++j)
         {
-            float s, c;
-            sincospif(2.0f * (float)j / (float)R, &s, &c);
-            wr[j].x = c;
-            wr[j].y = -s;
+            double s, c;
+            sincospi(2.0 * (double)j / (double)R, &s, &c);
+            wr[j].x = (T)c;
+            wr[j].y = (T)(-s);
         }
 
         // ---- columns, forward (the loads of all of a thread's columns are issued before any arithmetic) ----
@@ -130,8 +131,8 @@ namespace b200fft
             const long long es = a.in.es;
             if(a.in.planar)
             {
-                const float* __restrict__ p0 = reinterpret_cast<const float*>(a.in.p[0]);
-                const float* __restrict__ p1 = reinterpret_cast<const float*>(a.in.p[1]);
+                const T* __restrict__ p0 = reinterpret_cast<const T*>(a.in.p[0]);
+                const T* __restrict__ p1 = reinterpret_cast<const T*>(a.in.p[1]);
 #pragma unroll
                 for(int q = 0; q < ROUNDS; ++q)
 #pragma unroll
@@ -168,8 +169,8 @@ namespace b200fft
                     const bool live = tid + q * B::THREADS + CN * j < n;
                     const T2   x    = inverse ? cswap(v[q][j]) : v[q][j];
                     const T2   y    = cmul(x, ch[j]);
-                    v[q][j].x       = live ? y.x : 0.0f;
-                    v[q][j].y       = live ? y.y : 0.0f;
+                    v[q][j].x       = live ? y.x : (T)0;
+                    v[q][j].y       = live ? y.y : (T)0;
                 }
             }
 #pragma unroll
@@ -198,7 +199,7 @@ namespace b200fft
         // ---- rows: forward transform, filter, inverse transform; one warp per row ----
         {
             T2*    row = tile + warp * CN;
-            float* xw  = reinterpret_cast<float*>(row);
+            T*     xw  = reinterpret_cast<T*>(row);
             T2     r[32];
 #pragma unroll
             for(int j = 0; j < 32; ++j)
@@ -243,7 +244,7 @@ namespace b200fft
             tv[k] = twm[k * CN + tid];
 #pragma unroll
         for(int m2 = 0; m2 < H; ++m2)
-            cv[m2] = (tid + CN * m2 < n) ? chirp[tid + CN * m2] : make_float2(0.0f, 0.0f);
+            cv[m2] = (tid + CN * m2 < n) ? chirp[tid + CN * m2] : T2{(T)0, (T)0};
         __syncthreads();
 
         // ---- columns, inverse; outputs m2 < R/2 only ----
@@ -260,7 +261,7 @@ namespace b200fft
                         tv[k] = twm[k * CN + c];
 #pragma unroll
                     for(int m2 = 0; m2 < H; ++m2)
-                        cv[m2] = (c + CN * m2 < n) ? chirp[c + CN * m2] : make_float2(0.0f, 0.0f);
+                        cv[m2] = (c + CN * m2 < n) ? chirp[c + CN * m2] : T2{(T)0, (T)0};
                 }
                 T2 ev[H], od[H];
 #pragma unroll
@@ -292,7 +293,7 @@ namespace b200fft
     template <class C, int R>
     cudaError_t launch_bluestein_rc_kernel(const b200fft_kargs& a, unsigned long long ntiles, cudaStream_t stream)
     {
-        using B = BlueRC<R>;
+        using B = BlueRC<R, typename C::T>;
         static std::atomic<bool> attr_done[64]; // zero-initialised; host threads may launch the same kernel concurrently
         int                      dev = 0;
         cudaGetDevice(&dev);

@@ -766,7 +766,8 @@ namespace b200fft
                 size_t                    cnt = 0, best = 0;
                 const b200fft_pool_entry* p   = b200fft_pool(&cnt);
                 for(size_t i = 0; i < cnt; ++i)
-                    if(p[i].variant == B200FFT_ROW_BLUE && p[i].precision == prec_
+                    if((p[i].variant == B200FFT_ROW_BLUE || (p[i].variant == B200FFT_ROW_BLUE_RC && !getenv("ROCFFT_B200_NO_BLUE_RC")))
+                       && p[i].precision == prec_
                        && (size_t)p[i].length >= 2 * n - 1 && (!best || (size_t)p[i].length < best))
                         best = p[i].length;
                 return best;

@@ -169,12 +169,18 @@ def test_planner_choices_for_benchmark_configs(L, monkeypatch):
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)
     text = describe(L, p)
     assert "steps: 1" in text and "len20480_row_blue_rc" in text and p.work_bytes == 0
-    # ... other single-precision lengths pick the smallest padded length of whole 1024-point rows the same way,
-    # double precision and switched-off plans keep the three-pass kernel
+    # ... other lengths pick the smallest padded length of whole 1024-point rows the same way (double precision up to
+    # 12 rows: primes up to 6144 in one kernel, longer ones through the multi-kernel path); short lengths and
+    # switched-off plans keep the three-pass kernel
     for n, m in ((3001, 6144), (4099, 10240), (6007, 12288), (8191, 16384)):
         p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [n], 8)
-        assert f"len{m}_row_blue_rc" in describe(L, p), (n, describe(L, p))
-    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [4099], 8)
+        assert f"fft_sp_len{m}_row_blue_rc" in describe(L, p), (n, describe(L, p))
+    for n, m in ((3001, 6144), (4099, 10240), (6143, 12288)):
+        p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [n], 8)
+        assert f"fft_dp_len{m}_row_blue_rc" in describe(L, p) and p.work_bytes == 0, (n, describe(L, p))
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [6151], 8)
+    assert "bluestein_pad_mul" in describe(L, p)
+    p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 1, [1021], 8)
     assert "row_blue" in describe(L, p) and "row_blue_rc" not in describe(L, p)
     monkeypatch.setenv("ROCFFT_B200_NO_BLUE_RC", "1")
     p = rf.Plan(rf.rocfft_placement_notinplace, rf.rocfft_transform_type_complex_forward, 0, [10007], 4096)

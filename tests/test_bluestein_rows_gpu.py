@@ -1,4 +1,4 @@
-"""The row-per-warp Bluestein kernel (bluestein_rc.cuh; padded lengths R x 1024, R = 6 ... 20) against the CPU oracle:
+"""The row-per-warp Bluestein kernel (bluestein_rc.cuh; padded lengths R x 1024, R = 6 ... 20 in single and 6 ... 12 in double precision) against the CPU oracle:
 lengths across the range of the largest padded length, 8193 ... 10240 (primes, a composite outside the pool, the
 largest length it takes), one or two lengths for each of the smaller padded lengths,
 forward and inverse, in place and out of place, strided and planar layouts, scale factors, several
@@ -28,11 +28,17 @@ CASES = [
     Case(C2C_FWD, "single", [6007], 5, OOP),                     # 12 x 1024
     Case(C2C_FWD, "single", [8191], 3, IP),                      # 16 x 1024
     Case(C2C_INV, "single", [7919], 4, OOP, scale=0.5),
+    # double precision: padded lengths 6 ... 12 x 1024
+    Case(C2C_FWD, "double", [3001], 5, OOP),
+    Case(C2C_INV, "double", [4093], 3, IP),
+    Case(C2C_FWD, "double", [4099], 4, OOP, CP, CP),
+    Case(C2C_FWD, "double", [5119], 3, IP),
+    Case(C2C_INV, "double", [6143], 2, OOP, scale=0.25),
 ]
 
 
 def _plan_text(case):
-    p = rf.Plan(case.placement, case.ttype, 0, list(case.lengths), case.batch, scale=case.scale,
+    p = rf.Plan(case.placement, case.ttype, 0 if case.precision == "single" else 1, list(case.lengths), case.batch, scale=case.scale,
                 in_array_type=case.in_type, out_array_type=case.out_type, in_strides=case.in_strides, out_strides=case.out_strides,
                 in_distance=case.in_dist, out_distance=case.out_dist)
     t = p.describe()
