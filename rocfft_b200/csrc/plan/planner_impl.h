@@ -760,16 +760,28 @@ namespace b200fft
                 temp_release(mark);
             }
 
-            // smallest padded length >= 2n-1 that has a single-kernel Bluestein, or 0
+            // padded length >= 2n-1 of the single-kernel Bluestein that serves length n, or 0: the smallest one the
+            // pool has — except that a row-per-warp kernel (whole 1024-point rows) is taken over a three-pass kernel
+            // of a slightly shorter padded length (up to a quarter longer: measured 1.5-2 times faster at equal length)
             size_t fused_bluestein_length(size_t n) const
             {
-                size_t                    cnt = 0, best = 0;
+                size_t                    cnt = 0, best = 0, best_rc = 0;
                 const b200fft_pool_entry* p   = b200fft_pool(&cnt);
+                const bool                rc_ok = !getenv("ROCFFT_B200_NO_BLUE_RC");
                 for(size_t i = 0; i < cnt; ++i)
-                    if((p[i].variant == B200FFT_ROW_BLUE || (p[i].variant == B200FFT_ROW_BLUE_RC && !getenv("ROCFFT_B200_NO_BLUE_RC")))
-                       && p[i].precision == prec_
-                       && (size_t)p[i].length >= 2 * n - 1 && (!best || (size_t)p[i].length < best))
+                {
+                    if(p[i].precision != prec_ || (size_t)p[i].length < 2 * n - 1)
+                        continue;
+                    if(p[i].variant == B200FFT_ROW_BLUE && (!best || (size_t)p[i].length < best))
                         best = p[i].length;
+                    if(p[i].variant == B200FFT_ROW_BLUE_RC && rc_ok && (!best_rc || (size_t)p[i].length < best_rc))
+                        best_rc = p[i].length;
+                }
+                double prefer = 1.25;
+                if(const char* env = getenv("ROCFFT_B200_BLUE_RC_PREFER"))
+                    prefer = atof(env);
+                if(best_rc && (!best || (double)best_rc <= prefer * (double)best))
+                    return best_rc;
                 return best;
             }
 

@@ -28,6 +28,8 @@ CASES = [
     Case(C2C_FWD, "single", [6007], 5, OOP),                     # 12 x 1024
     Case(C2C_FWD, "single", [8191], 3, IP),                      # 16 x 1024
     Case(C2C_INV, "single", [7919], 4, OOP, scale=0.5),
+    Case(C2C_FWD, "single", [2503], 6, OOP),                     # 6 x 1024 preferred over the three-pass kernel at 5120
+    Case(C2C_INV, "double", [2557], 3, IP),
     # double precision: padded lengths 6 ... 12 x 1024
     Case(C2C_FWD, "double", [3001], 5, OOP),
     Case(C2C_INV, "double", [4093], 3, IP),
