@@ -149,6 +149,18 @@ def test_planner_choices_for_benchmark_configs(L, monkeypatch):
     text = describe(L, p)
     assert "steps: 3" in text and text.count("col_tma") == 2 and p.work_bytes == 0
     monkeypatch.delenv("ROCFFT_B200_NO_LONG_PITCH_PLAN")
+    # the work-array plan is for rows 4 MB or more apart along the slowest dimension of interleaved 3D volumes only
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 1, [512, 512, 512], 1)
+    assert p.work_bytes == 512 ** 3 * 16 and "temp+0" in describe(L, p)          # double precision: 4 MB pitch
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [512, 512, 512], 1)
+    assert p.work_bytes == 0                                                       # single precision: 2 MB pitch
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1,
+                in_array_type=rf.rocfft_array_type_complex_planar, out_array_type=rf.rocfft_array_type_complex_planar)
+    assert "temp+0" not in describe(L, p)                                          # planar: column kernels of the general kind
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1000], 1)
+    assert "temp+0" not in describe(L, p)                                          # 1000 has no TMA-fed column kernel
+    p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 512, 256], 3)
+    assert p.work_bytes == 3 * 1024 * 512 * 256 * 8                                # batches: one work volume per transform
     monkeypatch.setenv("ROCFFT_B200_2D_L2", "1")
     p = rf.Plan(rf.rocfft_placement_inplace, rf.rocfft_transform_type_complex_forward, 0, [1024, 1024, 1024], 1)
     text = describe(L, p)
